@@ -1,0 +1,124 @@
+// Split-KV merge: LSE = logsumexp_s lse_s, O = sum_s exp(lse_s - LSE) * O_s.
+//
+// One warp per output row.  The split LSEs are spread over the lanes and reduced with warp
+// shuffles (max, then sum of exponentials); each lane then owns D/32 consecutive output columns
+// and streams the fp32 partial rows with 8- or 16-byte loads, so a row of every split is one
+// fully coalesced 256/512-byte read.  HBM-bound: bytes = splits*rows*(D+1)*4 + rows*(2*D+4).
+//
+// Replaces kvcache_combine_kernel / kvcache_combine_kernel_legacy of the reference
+// (csrc/flash_attn/src/kvcache_native.cu:676-780); rows whose every split is empty get O = 0 and
+// LSE = 0 as there (:727).
+#include "combine.h"
+
+#include "ptx.cuh"
+
+namespace fa {
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+template <int D>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+combine_kernel(const float* __restrict__ o_accum, const float* __restrict__ lse_accum,
+               __half* __restrict__ o, float* __restrict__ lse, int64_t rows, int num_splits,
+               int h, int seqlen_q, int64_t o_batch_stride, int64_t o_row_stride,
+               int64_t o_head_stride) {
+  constexpr int kPerLane = D / 32;  // 2 or 4 consecutive columns
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (row >= rows) return;
+
+  // log-sum-exp over splits: lanes stride over the splits, shuffles reduce
+  float mx = -INFINITY;
+  for (int s = lane; s < num_splits; s += 32) mx = fmaxf(mx, lse_accum[s * rows + row]);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  float sum = 0.f;
+  if (mx != -INFINITY)
+    for (int s = lane; s < num_splits; s += 32) sum += __expf(lse_accum[s * rows + row] - mx);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  const bool empty = (mx == -INFINITY) || (sum == 0.f);
+  const float lse_total = empty ? -INFINITY : mx + __logf(sum);
+
+  float acc[kPerLane];
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) acc[i] = 0.f;
+  if (!empty) {
+    for (int s = 0; s < num_splits; ++s) {
+      const float ls = lse_accum[s * rows + row];  // same address for all lanes: one broadcast load
+      if (ls == -INFINITY) continue;
+      const float w = __expf(ls - lse_total);
+      const float* src = o_accum + (static_cast<int64_t>(s) * rows + row) * D + lane * kPerLane;
+      if constexpr (kPerLane == 4) {
+        const float4 x = *reinterpret_cast<const float4*>(src);
+        acc[0] = fmaf(w, x.x, acc[0]);
+        acc[1] = fmaf(w, x.y, acc[1]);
+        acc[2] = fmaf(w, x.z, acc[2]);
+        acc[3] = fmaf(w, x.w, acc[3]);
+      } else {
+        const float2 x = *reinterpret_cast<const float2*>(src);
+        acc[0] = fmaf(w, x.x, acc[0]);
+        acc[1] = fmaf(w, x.y, acc[1]);
+      }
+    }
+  }
+
+  // rows are ordered (b, h, seqlen_q)
+  const int64_t bh = row / seqlen_q;
+  const int q_pos = static_cast<int>(row - bh * seqlen_q);
+  const int64_t batch = bh / h;
+  const int head = static_cast<int>(bh - batch * h);
+  __half* dst = o + batch * o_batch_stride + q_pos * o_row_stride + head * o_head_stride +
+                lane * kPerLane;
+  if constexpr (kPerLane == 4) {
+    uint2 v;
+    v.x = pack_half2(acc[0], acc[1]);
+    v.y = pack_half2(acc[2], acc[3]);
+    *reinterpret_cast<uint2*>(dst) = v;
+  } else {
+    *reinterpret_cast<uint32_t*>(dst) = pack_half2(acc[0], acc[1]);
+  }
+  if (lse != nullptr && lane == 0) lse[row] = empty ? 0.f : lse_total;
+}
+
+}  // namespace
+
+int launch_combine(const float* o_accum, const float* lse_accum, void* o, float* lse, int64_t rows,
+                   int num_splits, int h, int seqlen_q, int d, int64_t o_batch_stride,
+                   int64_t o_row_stride, int64_t o_head_stride, cudaStream_t stream) {
+  if (rows == 0) return FA_OK;
+  const unsigned blocks = static_cast<unsigned>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  if (d == 128) {
+    combine_kernel<128><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
+        o_accum, lse_accum, static_cast<__half*>(o), lse, rows, num_splits, h, seqlen_q,
+        o_batch_stride, o_row_stride, o_head_stride);
+  } else {
+    combine_kernel<64><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
+        o_accum, lse_accum, static_cast<__half*>(o), lse, rows, num_splits, h, seqlen_q,
+        o_batch_stride, o_row_stride, o_head_stride);
+  }
+  FA_CHECK_CUDA(cudaGetLastError());
+  return FA_OK;
+}
+
+}  // namespace fa
+
+extern "C" int fa_combine(const FaCombineParams* p, fa_stream_t stream) {
+  using namespace fa;
+  FA_CHECK_ARG(p != nullptr, "fa_combine: params is NULL");
+  FA_CHECK_ARG(p->o_accum && p->lse_accum && p->o, "fa_combine: o_accum, lse_accum, o must be non-NULL");
+  if (p->d != 64 && p->d != 128)
+    return set_error(FA_ERR_UNSUPPORTED, "fa_combine: head_dim must be 64 or 128");
+  FA_CHECK_ARG(p->num_splits >= 1 && p->b >= 0 && p->h >= 1 && p->seqlen_q >= 0,
+               "fa_combine: bad sizes");
+  FA_CHECK_ARG(aligned16(p->o_accum) && (reinterpret_cast<uintptr_t>(p->o) & 7) == 0 &&
+                   p->o_row_stride % 4 == 0 && p->o_head_stride % 4 == 0 && p->o_batch_stride % 4 == 0,
+               "fa_combine: o_accum must be 16-byte aligned, o 8-byte aligned with strides multiple of 4");
+  int rc = check_device_sm100();
+  if (rc != FA_OK) return rc;
+  const int64_t rows = static_cast<int64_t>(p->b) * p->h * p->seqlen_q;
+  return launch_combine(p->o_accum, p->lse_accum, p->o, p->lse, rows, p->num_splits, p->h,
+                        p->seqlen_q, p->d, p->o_batch_stride, p->o_row_stride, p->o_head_stride,
+                        static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,546 @@
+// Forward attention for sm_100a: O = softmax(Q K^T * scale [+ causal]) V and LSE.
+//
+// One CTA owns 256 query rows of one (sequence, query head): two 128-row Q tiles that share every
+// K/V block, so the tensor core always has the other tile's GEMMs to run while one tile is in its
+// softmax.  Warp roles (320 threads):
+//   warps 0-3  softmax of Q tile 0, one thread per query row (TMEM lane)
+//   warps 4-7  softmax of Q tile 1
+//   warp  8    TMA producer: Q tiles once, then K and V blocks through a ring of stages
+//   warp  9    tcgen05.mma issuer (one thread); also owns the TMEM allocation
+// Both GEMMs run on tcgen05 with fp32 accumulators in TMEM:
+//   S_t = Q_t K_j^T   A and B from shared memory (K-major, 128-byte swizzle as TMA writes them)
+//   O_t += P_t V_j    A = P_t read from TMEM (fp16, aliased onto S_t), B = V_j from shared memory
+//                     as an MN-major operand (V is stored keys x head_dim)
+// TMEM columns: S_0 [0,128) S_1 [128,256) O_0 [256,256+D) O_1 [256+D,256+2D).
+// The softmax keeps a lazily updated reference maximum: O and the row sum are rescaled only when
+// the running maximum grew by more than 2^8 relative to the reference, which keeps P within fp16
+// range and removes almost all rescale passes over O.
+//
+// Replaces flash_fwd_kernel / compute_attn_1rowblock of the reference
+// (csrc/flash_attn/src/flash_fwd_kernel.h:23-664) including its masking (src/mask.h:20-69) and
+// varlen offsets (src/block_info.h:3-36).
+#include "common.h"
+#include "ptx.cuh"
+
+namespace fa {
+
+namespace {
+
+constexpr int kBlockM = 128;   // rows per Q tile
+constexpr int kTiles = 2;      // Q tiles per CTA
+constexpr int kBlockN = 128;   // keys per K/V block
+constexpr int kNumThreads = 320;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct FwdKernelParams {
+  CUtensorMap tm_q;
+  CUtensorMap tm_k;
+  CUtensorMap tm_v;
+  __half* o;
+  float* lse;
+  int64_t o_batch_stride, o_row_stride, o_head_stride;
+  int64_t lse_row_stride;
+  int seqlen_q, seqlen_k;
+  int h, h_k;
+  float scale;       // softmax scale
+  float scale_log2;  // softmax scale * log2(e)
+  int is_causal;
+  const int* cu_seqlens_q;
+  const int* cu_seqlens_k;
+  const int* seqused_k;
+  const int* cache_batch_idx;
+  const int* block_table;
+  int64_t block_table_batch_stride;
+  int page_size;
+  int* status;
+};
+
+template <int D>
+struct Cfg {
+  static constexpr int kChunks = D / 64;              // 128-byte swizzle chunks per row
+  static constexpr int kChunkBytes = 128 * 128;       // 128 rows x 128 B
+  static constexpr int kTileBytes = kChunks * kChunkBytes;
+  static constexpr int kStages = (D == 128) ? 2 : 4;
+  static constexpr int kColS = 0;                     // + 128 * tile
+  static constexpr int kColO = 256;                   // + D * tile
+  static constexpr int kTmemCols = 512;
+  static constexpr int kSmemBytes =
+      kTiles * kTileBytes + 2 * kStages * kTileBytes + 1024 /*barriers*/ + 1024 /*alignment*/;
+};
+
+struct Barriers {
+  uint64_t q_full[kTiles];
+  uint64_t s_full[kTiles];
+  uint64_t p_full[kTiles];
+  uint64_t o_full[kTiles];
+  uint64_t k_full[4];
+  uint64_t k_empty[4];
+  uint64_t v_full[4];
+  uint64_t v_empty[4];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ bool wait_all(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
+  bool ok = mbar_wait(bar, parity, ctx);
+  return __all_sync(0xffffffffu, ok);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kNumThreads, 1)
+fwd_kernel(const __grid_constant__ FwdKernelParams p) {
+  using C = Cfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+
+  // ---- which rows does this CTA own? (decided before any resource is taken) ----
+  const int batch = blockIdx.z;
+  const int head = blockIdx.y;
+  const int mpair = gridDim.x - 1 - blockIdx.x;  // heavy (late-row) causal tiles first
+  const bool varlen_q = p.cu_seqlens_q != nullptr;
+  const bool varlen_k = p.cu_seqlens_k != nullptr;
+  const int q_off = varlen_q ? p.cu_seqlens_q[batch] : 0;
+  const int sq = varlen_q ? p.cu_seqlens_q[batch + 1] - q_off : p.seqlen_q;
+  const int k_off = varlen_k ? p.cu_seqlens_k[batch] : 0;
+  int sk = varlen_k ? p.cu_seqlens_k[batch + 1] - k_off : p.seqlen_k;
+  if (p.seqused_k) sk = p.seqused_k[batch];
+  const int row0 = mpair * (kTiles * kBlockM);
+  if (row0 >= sq) return;
+  if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;
+
+  const int bq = varlen_q ? 0 : batch;
+  const int bk = varlen_k ? 0 : (p.cache_batch_idx ? p.cache_batch_idx[batch] : batch);
+  const int head_k = head / (p.h / p.h_k);
+
+  // number of K/V blocks each tile visits
+  const int nkb = (sk + kBlockN - 1) / kBlockN;
+  int nb[kTiles];
+#pragma unroll
+  for (int t = 0; t < kTiles; ++t) {
+    const int r0 = row0 + t * kBlockM;
+    int n = nkb;
+    if (p.is_causal) {
+      const int x = r0 + kBlockM + sk - sq;  // one past the last visible key of the tile's last row
+      n = x <= 0 ? 0 : min(nkb, (x + kBlockN - 1) / kBlockN);
+    }
+    if (r0 >= sq) n = 0;
+    nb[t] = n;
+  }
+  const int nb_max = max(nb[0], nb[1]);
+
+  // ---- shared memory carve-up (1024-byte aligned tiles for the 128-byte swizzle) ----
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + kTiles * C::kTileBytes;
+  uint8_t* sV = sK + C::kStages * C::kTileBytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(sV + C::kStages * C::kTileBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int t = 0; t < kTiles; ++t) {
+      mbar_init(&bars->q_full[t], 1);
+      mbar_init(&bars->s_full[t], 1);
+      mbar_init(&bars->p_full[t], 128);
+      mbar_init(&bars->o_full[t], 1);
+    }
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->v_empty[s], 1);
+    }
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(&bars->tmem_base, C::kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == kProducerWarp && lane == 0) {
+    prefetch_tensormap(&p.tm_q);
+    prefetch_tensormap(&p.tm_k);
+    prefetch_tensormap(&p.tm_v);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+  WaitCtx ctx{&bars->abort_flag, p.status};
+
+  if (warp == kProducerWarp) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) {
+#pragma unroll
+      for (int t = 0; t < kTiles; ++t) {
+        if (nb[t] > 0) {
+          mbar_arrive_expect_tx(&bars->q_full[t], C::kTileBytes);
+#pragma unroll
+          for (int c = 0; c < C::kChunks; ++c)
+            tma_load_4d(sQ + t * C::kTileBytes + c * C::kChunkBytes, &p.tm_q, &bars->q_full[t],
+                        c * 64, head, q_off + row0 + t * kBlockM, bq);
+        }
+      }
+      for (int j = 0; j < nb_max; ++j) {
+        const int s = j % C::kStages;
+        const uint32_t ph = (j / C::kStages) & 1;
+        int krow = k_off + j * kBlockN;
+        int kb = bk;
+        if (p.block_table) {
+          const int tok = j * kBlockN;
+          kb = p.block_table[batch * p.block_table_batch_stride + tok / p.page_size];
+          krow = tok % p.page_size;
+        }
+        if (!mbar_wait(&bars->k_empty[s], ph ^ 1, ctx)) break;
+        mbar_arrive_expect_tx(&bars->k_full[s], C::kTileBytes);
+#pragma unroll
+        for (int c = 0; c < C::kChunks; ++c)
+          tma_load_4d(sK + s * C::kTileBytes + c * C::kChunkBytes, &p.tm_k, &bars->k_full[s],
+                      c * 64, head_k, krow, kb);
+        if (!mbar_wait(&bars->v_empty[s], ph ^ 1, ctx)) break;
+        mbar_arrive_expect_tx(&bars->v_full[s], C::kTileBytes);
+#pragma unroll
+        for (int c = 0; c < C::kChunks; ++c)
+          tma_load_4d(sV + s * C::kTileBytes + c * C::kChunkBytes, &p.tm_v, &bars->v_full[s],
+                      c * 64, head_k, krow, kb);
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_f16(128, kBlockN, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_f16(128, D, false, true);
+      const uint32_t sQ_addr = smem_u32(sQ);
+      const uint32_t sK_addr = smem_u32(sK);
+      const uint32_t sV_addr = smem_u32(sV);
+
+      // S_t = Q_t K_j^T : D/16 MMAs of K=16; slice k lives in swizzle chunk k/4 at byte (k%4)*32.
+      auto issue_qk = [&](int t, int j) {
+        const int s = j % C::kStages;
+        const uint32_t qa = sQ_addr + t * C::kTileBytes;
+        const uint32_t ka = sK_addr + s * C::kTileBytes;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * C::kChunkBytes + (k & 3) * 32;
+          mma_ss(tmem_base + C::kColS + t * 128, make_smem_desc(qa + off, 16, 1024),
+                 make_smem_desc(ka + off, 16, 1024), idesc_qk, k > 0);
+        }
+      };
+      // O_t += P_t V_j : 8 MMAs of K=16 keys; A slice k = 8 TMEM columns of packed fp16; B slice k
+      // starts 16 key rows (2048 B) further, head_dim chunks are kChunkBytes apart (LBO).
+      auto issue_pv = [&](int t, int j) {
+        const int s = j % C::kStages;
+        const uint32_t va = sV_addr + s * C::kTileBytes;
+#pragma unroll
+        for (int k = 0; k < kBlockN / 16; ++k) {
+          mma_ts(tmem_base + C::kColO + t * D, tmem_base + C::kColS + t * 128 + k * 8,
+                 make_smem_desc(va + k * 2048, C::kChunkBytes, 1024), idesc_pv, (j > 0) || (k > 0));
+        }
+      };
+
+      bool ok = true;
+#pragma unroll
+      for (int t = 0; t < kTiles; ++t)
+        if (nb[t] > 0) ok = ok && mbar_wait(&bars->q_full[t], 0, ctx);
+      if (ok && nb_max > 0) {
+        ok = mbar_wait(&bars->k_full[0], 0, ctx);
+        if (ok) {
+          tc_fence_after_sync();
+#pragma unroll
+          for (int t = 0; t < kTiles; ++t) {
+            if (nb[t] > 0) {
+              issue_qk(t, 0);
+              tc_commit(&bars->s_full[t]);
+            }
+          }
+          tc_commit(&bars->k_empty[0]);
+        }
+      }
+      for (int j = 0; ok && j < nb_max; ++j) {
+        const int s = j % C::kStages;
+        const uint32_t ph = (j / C::kStages) & 1;
+        const int s1 = (j + 1) % C::kStages;
+        const uint32_t ph1 = ((j + 1) / C::kStages) & 1;
+#pragma unroll
+        for (int t = 0; t < kTiles; ++t) {
+          if (j >= nb[t]) continue;
+          if (!(ok = mbar_wait(&bars->p_full[t], j & 1, ctx))) break;
+          if (!(ok = mbar_wait(&bars->v_full[s], ph, ctx))) break;
+          tc_fence_after_sync();
+          issue_pv(t, j);
+          const bool last_user_v = (t == kTiles - 1) || !(j < nb[kTiles - 1]);
+          if (last_user_v) tc_commit(&bars->v_empty[s]);
+          if (j + 1 < nb[t]) {
+            if (!(ok = mbar_wait(&bars->k_full[s1], ph1, ctx))) break;
+            tc_fence_after_sync();
+            issue_qk(t, j + 1);
+            tc_commit(&bars->s_full[t]);
+            const bool last_user_k = (t == kTiles - 1) || !(j + 1 < nb[kTiles - 1]);
+            if (last_user_k) tc_commit(&bars->k_empty[s1]);
+          } else {
+            tc_commit(&bars->o_full[t]);
+          }
+        }
+      }
+    }
+  } else {
+    // =========================== softmax + epilogue ===========================
+    const int t = warp >> 2;                 // Q tile of this warpgroup
+    const int quarter = warp & 3;            // TMEM lane quarter this warp may access
+    const int row_in_tile = quarter * 32 + lane;
+    const int row = row0 + t * kBlockM + row_in_tile;  // row within the sequence
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t tS = tmem_base + lane_base + C::kColS + t * 128;
+    const uint32_t tO = tmem_base + lane_base + C::kColO + t * D;
+    const int nbt = nb[t];
+    const float c = p.scale_log2;
+
+    float m_ref = -INFINITY;
+    float l = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < nbt; ++j) {
+      if (!(ok = wait_all(&bars->s_full[t], j & 1, ctx))) break;
+      tc_fence_after_sync();
+      uint32_t sr[4][32];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) tmem_ld32(tS + q * 32, sr[q]);
+      tmem_wait_ld();
+
+      // masking: only blocks that touch the sequence end or the causal diagonal
+      const int col0 = j * kBlockN;
+      int limit = sk - 1 - col0;  // last visible column index within this block
+      if (p.is_causal) limit = min(limit, row + sk - sq - col0);
+      if (limit < kBlockN - 1) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (q * 32 + i > limit) sr[q][i] = 0xff800000u;  // -inf
+      }
+
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        mx0 = fmaxf(mx0, __uint_as_float(sr[0][i]));
+        mx1 = fmaxf(mx1, __uint_as_float(sr[1][i]));
+        mx2 = fmaxf(mx2, __uint_as_float(sr[2][i]));
+        mx3 = fmaxf(mx3, __uint_as_float(sr[3][i]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+
+      // lazy reference maximum
+      float alpha = 1.f;
+      bool need = false;
+      if (j == 0) {
+        m_ref = mx;
+      } else if (mx > m_ref) {
+        if (m_ref == -INFINITY) {
+          m_ref = mx;  // nothing accumulated yet for this row: O and l are exactly 0
+        } else if ((mx - m_ref) * c > kRescaleThreshold) {
+          alpha = ex2f((m_ref - mx) * c);
+          m_ref = mx;
+          need = true;
+        }
+      }
+      if (__any_sync(0xffffffffu, need)) {
+        l *= alpha;
+#pragma unroll
+        for (int q = 0; q < D / 32; ++q) {
+          uint32_t orr[32];
+          tmem_ld32(tO + q * 32, orr);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+          tmem_st32(tO + q * 32, orr);
+        }
+      }
+
+      const float neg_mc = (m_ref == -INFINITY) ? 0.f : -m_ref * c;
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = ex2f(fmaf(__uint_as_float(sr[q][2 * i]), c, neg_mc));
+          const float p1 = ex2f(fmaf(__uint_as_float(sr[q][2 * i + 1]), c, neg_mc));
+          l0 += p0;
+          l1 += p1;
+          pk[i] = pack_half2(p0, p1);
+        }
+        tmem_st16(tS + q * 16, pk);
+      }
+      l += l0 + l1;
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->p_full[t]);
+    }
+
+    // ---- epilogue: normalise, convert, store ----
+    const bool row_valid = row < sq;
+    int64_t o_index;
+    if (varlen_q) {
+      o_index = static_cast<int64_t>(q_off + row) * p.o_row_stride + head * p.o_head_stride;
+    } else {
+      o_index = batch * p.o_batch_stride + static_cast<int64_t>(row) * p.o_row_stride +
+                head * p.o_head_stride;
+    }
+    __half* orow = p.o + o_index;
+    if (ok && nbt > 0) ok = wait_all(&bars->o_full[t], 0, ctx);
+    if (ok && row0 + t * kBlockM < sq) {
+      float lse_val = 0.f;
+      float inv = 0.f;
+      if (nbt > 0 && l > 0.f && m_ref != -INFINITY) {
+        inv = 1.f / l;
+        lse_val = (m_ref * c + __log2f(l)) * kLn2;
+      }
+      if (nbt > 0) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int q = 0; q < D / 32; ++q) {
+          uint32_t orr[32];
+          tmem_ld32(tO + q * 32, orr);
+          tmem_wait_ld();
+          if (row_valid) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 v;
+              v.x = pack_half2(__uint_as_float(orr[8 * i + 0]) * inv, __uint_as_float(orr[8 * i + 1]) * inv);
+              v.y = pack_half2(__uint_as_float(orr[8 * i + 2]) * inv, __uint_as_float(orr[8 * i + 3]) * inv);
+              v.z = pack_half2(__uint_as_float(orr[8 * i + 4]) * inv, __uint_as_float(orr[8 * i + 5]) * inv);
+              v.w = pack_half2(__uint_as_float(orr[8 * i + 6]) * inv, __uint_as_float(orr[8 * i + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + q * 32 + i * 8) = v;
+            }
+          }
+        }
+      } else if (row_valid) {
+        // no key block is visible to any row of this tile (causal with seqlen_q > seqlen_k)
+        const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) *reinterpret_cast<uint4*>(orow + i * 8) = z;
+      }
+      if (row_valid)
+        p.lse[(static_cast<int64_t>(batch) * p.h + head) * p.lse_row_stride + row] = lse_val;
+    }
+  }
+
+  // ---- common exit ----
+  tc_fence_before_sync();
+  __syncthreads();
+  if (bars->abort_flag) {
+    // let TMA copies that may still be in flight land before the shared memory is released
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) {
+    }
+    __syncthreads();
+  }
+  if (warp == kMmaWarp) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+template <int D>
+int launch_fwd(const FwdKernelParams& kp, int b, int h, int seqlen_q, cudaStream_t stream) {
+  using C = Cfg<D>;
+  static bool configured[64] = {};
+  int dev = 0;
+  FA_CHECK_CUDA(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    FA_CHECK_CUDA(cudaFuncSetAttribute(fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       C::kSmemBytes));
+    configured[dev & 63] = true;
+  }
+  dim3 grid((seqlen_q + kTiles * kBlockM - 1) / (kTiles * kBlockM), h, b);
+  fwd_kernel<D><<<grid, kNumThreads, C::kSmemBytes, stream>>>(kp);
+  FA_CHECK_CUDA(cudaGetLastError());
+  return FA_OK;
+}
+
+}  // namespace
+}  // namespace fa
+
+extern "C" int fa_fwd(const FaFwdParams* p, fa_stream_t stream_) {
+  using namespace fa;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  FA_CHECK_ARG(p != nullptr, "fa_fwd: params is NULL");
+  FA_CHECK_ARG(p->q && p->k && p->v && p->o && p->lse, "fa_fwd: q, k, v, o, lse must be non-NULL");
+  if (p->d != 64 && p->d != 128)
+    return set_error(FA_ERR_UNSUPPORTED, "fa_fwd: head_dim must be 64 or 128");
+  FA_CHECK_ARG(p->b >= 1 && p->h >= 1 && p->h_k >= 1, "fa_fwd: b, h, h_k must be positive");
+  FA_CHECK_ARG(p->h % p->h_k == 0, "fa_fwd: h must be divisible by h_k");
+  FA_CHECK_ARG(p->seqlen_q >= 1 && p->seqlen_k >= 0, "fa_fwd: bad sequence lengths");
+  FA_CHECK_ARG((p->cu_seqlens_q == nullptr) == (p->cu_seqlens_k == nullptr) || p->cu_seqlens_k == nullptr,
+               "fa_fwd: cu_seqlens_k requires cu_seqlens_q");
+  FA_CHECK_ARG(aligned16(p->o) && p->o_row_stride % 8 == 0 && p->o_head_stride % 8 == 0 &&
+                   (p->cu_seqlens_q || p->o_batch_stride % 8 == 0),
+               "fa_fwd: o must be 16-byte aligned with strides that are multiples of 8 elements");
+  FA_CHECK_ARG(p->lse_row_stride >= p->seqlen_q, "fa_fwd: lse_row_stride is smaller than seqlen_q");
+  if (p->block_table) {
+    FA_CHECK_ARG(p->page_size >= 128 && p->page_size % 128 == 0,
+                 "fa_fwd: page_size must be a positive multiple of 128");
+    FA_CHECK_ARG(!p->cu_seqlens_k && !p->cache_batch_idx,
+                 "fa_fwd: block_table excludes cu_seqlens_k and cache_batch_idx");
+    FA_CHECK_ARG(p->seqused_k != nullptr, "fa_fwd: block_table requires seqused_k");
+  }
+  int rc = check_device_sm100();
+  if (rc != FA_OK) return rc;
+
+  FwdKernelParams kp;
+  const bool varlen_q = p->cu_seqlens_q != nullptr;
+  const bool varlen_k = p->cu_seqlens_k != nullptr;
+  const int64_t q_rows = varlen_q ? p->total_q : p->seqlen_q;
+  const int64_t q_batch = varlen_q ? 1 : p->b;
+  FA_CHECK_ARG(q_rows >= 1, "fa_fwd: q has no rows");
+  rc = make_tensor_map_4d(&kp.tm_q, p->q, p->d, p->h, q_rows, q_batch, p->q_head_stride,
+                          p->q_row_stride, p->q_batch_stride, kBlockM, "fa_fwd: q");
+  if (rc != FA_OK) return rc;
+  int64_t k_rows, k_batch;
+  if (p->block_table) {
+    k_rows = p->page_size;
+    k_batch = p->k_batch;
+  } else if (varlen_k) {
+    k_rows = p->total_k;
+    k_batch = 1;
+  } else {
+    k_rows = p->seqlen_k;
+    k_batch = p->k_batch > 0 ? p->k_batch : p->b;
+  }
+  if (k_rows < 1) k_rows = 1;  // seqlen_k == 0: nothing is ever loaded
+  rc = make_tensor_map_4d(&kp.tm_k, p->k, p->d, p->h_k, k_rows, k_batch, p->k_head_stride,
+                          p->k_row_stride, p->k_batch_stride, kBlockN, "fa_fwd: k");
+  if (rc != FA_OK) return rc;
+  rc = make_tensor_map_4d(&kp.tm_v, p->v, p->d, p->h_k, k_rows, k_batch, p->v_head_stride,
+                          p->v_row_stride, p->v_batch_stride, kBlockN, "fa_fwd: v");
+  if (rc != FA_OK) return rc;
+
+  kp.o = static_cast<__half*>(p->o);
+  kp.lse = p->lse;
+  kp.o_batch_stride = p->o_batch_stride;
+  kp.o_row_stride = p->o_row_stride;
+  kp.o_head_stride = p->o_head_stride;
+  kp.lse_row_stride = p->lse_row_stride;
+  kp.seqlen_q = p->seqlen_q;
+  kp.seqlen_k = p->seqlen_k;
+  kp.h = p->h;
+  kp.h_k = p->h_k;
+  kp.scale = p->softmax_scale;
+  kp.scale_log2 = p->softmax_scale * kLog2e;
+  kp.is_causal = p->is_causal;
+  kp.cu_seqlens_q = p->cu_seqlens_q;
+  kp.cu_seqlens_k = p->cu_seqlens_k;
+  kp.seqused_k = p->seqused_k;
+  kp.cache_batch_idx = p->cache_batch_idx;
+  kp.block_table = p->block_table;
+  kp.block_table_batch_stride = p->block_table_batch_stride;
+  kp.page_size = p->page_size;
+  kp.status = device_status_ptr();
+
+  if (p->d == 128) return launch_fwd<128>(kp, p->b, p->h, p->seqlen_q, stream);
+  return launch_fwd<64>(kp, p->b, p->h, p->seqlen_q, stream);
+}

@@ -1,0 +1,203 @@
+/*
+ * fa_b200.h -- C ABI of the B200 (sm_100a) FlashAttention launcher library `libfa_b200.so`.
+ *
+ * Every entry point takes plain pointers and sizes (no torch types), enqueues its kernels on the
+ * stream it is given and returns without synchronising the host.  Return value: 0 on success, a
+ * negative FA_ERR_* code otherwise; fa_last_error() returns the message of the calling thread's
+ * last failure.  Invalid arguments are rejected on the host before any launch.  Unless stated
+ * otherwise an entry point allocates nothing: outputs and scratch memory are owned by the caller.
+ *
+ * Each declaration names the reference interface it replaces (paths inside the reference project
+ * Cy-47/flash-attention-turing).
+ *
+ * Tensor conventions: fp16 (IEEE half) data, fp32 log-sum-exp, int32 index arrays, all in device
+ * memory.  Strides are in ELEMENTS and 64-bit; the innermost (head_dim) stride is always 1.
+ * head_dim is 64 or 128.  Causal masking is bottom-right aligned: key j is visible to query i iff
+ * j <= i + seqlen_k - seqlen_q.  A query row without a visible key gets O = 0 and LSE = 0.
+ */
+#ifndef FA_B200_H_
+#define FA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Same underlying type as cudaStream_t (struct CUstream_st*); void* keeps the header CUDA-free. */
+typedef void* fa_stream_t;
+
+enum {
+  FA_OK = 0,
+  FA_ERR_INVALID_ARGUMENT = -1, /* shape / stride / pointer check failed on the host          */
+  FA_ERR_UNSUPPORTED = -2,      /* head_dim not in {64,128}, wrong GPU architecture, ...       */
+  FA_ERR_WORKSPACE = -3,        /* caller-provided scratch buffer is too small                 */
+  FA_ERR_CUDA = -4              /* a CUDA runtime/driver call or the launch itself failed      */
+};
+
+/* Text of the calling thread's last error ("" if none). The pointer stays valid until the next
+ * failing call on the same thread. */
+const char* fa_last_error(void);
+
+/* ABI version of this header; bumped on incompatible struct changes. */
+int fa_abi_version(void);
+
+/* Kernels never trap: every device-side wait (mbarrier, pipeline stage) is bounded, and a wait that
+ * gives up records a non-zero code in a per-device status word and lets the kernel return.  This
+ * call synchronises the current device and returns that word (0 = no kernel reported a problem,
+ * 1 = a wait timed out and the outputs of that launch are invalid, negative = FA_ERR_*).  With
+ * reset != 0 the word is cleared afterwards.  No counterpart in the reference, whose launches are
+ * not error-checked at all (src/flash_fwd_launch_template.h:73-89). */
+int fa_device_status(int reset);
+
+/* ------------------------------------------------------------------------------------------- */
+/* Forward: O = softmax(Q K^T * scale [+ causal mask]) V, LSE = logsumexp of the scaled scores.  */
+/* Replaces mha_fwd / mha_varlen_fwd (csrc/flash_attn/flash_api.cpp:188-256, 353-416), the param */
+/* struct Flash_fwd_params (csrc/flash_attn/src/flash.h:38-60), run_flash_fwd                    */
+/* (src/flash_fwd_launch_template.h:49-93) and flash_fwd_kernel (src/flash_fwd_kernel.h:23-664). */
+/* Also serves the tiled path of mha_fwd_kvcache (flash_api.cpp:686-714) through seqused_k,      */
+/* cache_batch_idx and block_table, without the index_select copy the reference makes.           */
+/* ------------------------------------------------------------------------------------------- */
+typedef struct FaFwdParams {
+  const void* q; /* dense (b, seqlen_q, h, d); varlen (total_q, h, d)                           */
+  const void* k; /* dense (b_k, seqlen_k, h_k, d); varlen (total_k, h_k, d); paged (pages, page_size, h_k, d) */
+  const void* v;
+  void* o;       /* same layout family as q                                                    */
+  float* lse;    /* (b, h, lse_row_stride) fp32, lse_row_stride >= seqlen_q                      */
+  int64_t q_batch_stride, q_row_stride, q_head_stride;
+  int64_t k_batch_stride, k_row_stride, k_head_stride;
+  int64_t v_batch_stride, v_row_stride, v_head_stride;
+  int64_t o_batch_stride, o_row_stride, o_head_stride;
+  int64_t lse_row_stride;      /* elements between consecutive (b, h) rows of lse               */
+  int32_t b;                   /* number of sequences                                           */
+  int32_t seqlen_q, seqlen_k;  /* dense: exact; varlen: max_seqlen_q / max_seqlen_k             */
+  int32_t h, h_k, d;
+  int32_t total_q, total_k;    /* varlen only: rows of the packed q / k tensors                 */
+  int32_t k_batch;             /* rows of dim 0 of k/v (cache batch or number of pages)         */
+  float softmax_scale;
+  int32_t is_causal;
+  const int32_t* cu_seqlens_q; /* (b+1) or NULL (dense)                                         */
+  const int32_t* cu_seqlens_k; /* (b+1) or NULL                                                 */
+  const int32_t* seqused_k;    /* (b) keys actually used per sequence, or NULL                  */
+  const int32_t* cache_batch_idx; /* (b) row of k/v dim 0 used by sequence i, or NULL           */
+  const int32_t* block_table;  /* (b, block_table_batch_stride) page ids, or NULL               */
+  int64_t block_table_batch_stride;
+  int32_t page_size;           /* tokens per page (multiple of 128) when block_table != NULL    */
+  int32_t reserved0;
+} FaFwdParams;
+
+int fa_fwd(const FaFwdParams* p, fa_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------- */
+/* Backward: dQ, dK, dV from dO (and O, LSE of the forward).                                    */
+/* Replaces mha_bwd / mha_varlen_bwd (flash_api.cpp:258-351, 418-506), Flash_bwd_params          */
+/* (flash.h:62-83), run_flash_bwd (src/flash_bwd_launch_template.h:69-146) and its three kernels */
+/* (flash_bwd_preprocess_kernel.h:23-96, flash_bwd_kernel.h:25-609 and :613-1344).  dK and dV    */
+/* are written per KV head; the per-query-head buffers and the torch::sum_out reduction of the   */
+/* reference (flash_api.cpp:338-348) do not exist here.                                          */
+/* Scratch: `workspace` must hold fa_bwd_workspace_bytes() bytes (fp32 rowsum(dO*O) and the LSE  */
+/* in base-2 units).                                                                             */
+/* ------------------------------------------------------------------------------------------- */
+typedef struct FaBwdParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;
+  const void* dout;
+  const float* lse;
+  void* dq;
+  void* dk;
+  void* dv;
+  int64_t q_batch_stride, q_row_stride, q_head_stride;
+  int64_t k_batch_stride, k_row_stride, k_head_stride;
+  int64_t v_batch_stride, v_row_stride, v_head_stride;
+  int64_t o_batch_stride, o_row_stride, o_head_stride;
+  int64_t do_batch_stride, do_row_stride, do_head_stride;
+  int64_t dq_batch_stride, dq_row_stride, dq_head_stride;
+  int64_t dk_batch_stride, dk_row_stride, dk_head_stride;
+  int64_t dv_batch_stride, dv_row_stride, dv_head_stride;
+  int64_t lse_row_stride;
+  int32_t b, seqlen_q, seqlen_k, h, h_k, d;
+  int32_t total_q, total_k;
+  float softmax_scale;
+  int32_t is_causal;
+  const int32_t* cu_seqlens_q;
+  const int32_t* cu_seqlens_k;
+  void* workspace;
+  size_t workspace_bytes;
+} FaBwdParams;
+
+size_t fa_bwd_workspace_bytes(const FaBwdParams* p);
+int fa_bwd(const FaBwdParams* p, fa_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------- */
+/* KV-cache step: append k_new/v_new in place at cache_seqlens, then attend q against            */
+/* [0, cache_seqlens + seqlen_new) with split-KV and the LSE combine.                           */
+/* Replaces mha_fwd_kvcache (flash_api.cpp:508-715), run_kvcache_paged_append /                  */
+/* paged_append_kernel (src/kvcache_native.cu:782-871, 956-993), run_mha_fwd_kvcache_native      */
+/* (:995-1218) with kvcache_decode_split_kernel / kvcache_split_kernel /                         */
+/* kvcache_split_kernel_legacy (:148-674) and kvcache_combine_kernel (:676-780).                 */
+/* No host synchronisation: the capacity check of the reference (flash_api.cpp:627) is the       */
+/* caller's responsibility.  num_splits == 0 selects a split count from the shape                */
+/* (choose_num_splits, kvcache_native.cu:913-952, retuned for 148 SMs).                          */
+/* Scratch: fa_kvcache_workspace_bytes() bytes when the effective split count exceeds 1.         */
+/* ------------------------------------------------------------------------------------------- */
+typedef struct FaKvcacheParams {
+  const void* q;       /* (b, seqlen_q, h, d)                                                   */
+  void* k_cache;       /* contiguous (b_cache, seqlen_cache, h_k, d) or paged (pages, page_size, h_k, d) */
+  void* v_cache;
+  const void* k_new;   /* (b, seqlen_new, h_k, d) or NULL                                        */
+  const void* v_new;
+  void* o;             /* (b, seqlen_q, h, d)                                                   */
+  float* lse;          /* (b, h, seqlen_q)                                                      */
+  int64_t q_batch_stride, q_row_stride, q_head_stride;
+  int64_t kc_batch_stride, kc_row_stride, kc_head_stride;
+  int64_t vc_batch_stride, vc_row_stride, vc_head_stride;
+  int64_t kn_batch_stride, kn_row_stride, kn_head_stride;
+  int64_t vn_batch_stride, vn_row_stride, vn_head_stride;
+  int64_t o_batch_stride, o_row_stride, o_head_stride;
+  int32_t b, seqlen_q, seqlen_new, h, h_k, d;
+  int32_t cache_batch;         /* dim 0 of the cache tensors (cache rows or pages)              */
+  int32_t seqlen_cache;        /* dim 1 of the cache tensors (capacity per row, or page size)   */
+  float softmax_scale;
+  int32_t is_causal;
+  const int32_t* cache_seqlens;    /* (b) tokens in the cache BEFORE the append                 */
+  const int32_t* cache_batch_idx;  /* (b) or NULL; contiguous cache only                        */
+  const int32_t* block_table;      /* (b, block_table_batch_stride) or NULL                     */
+  int64_t block_table_batch_stride;
+  int32_t max_blocks_per_seq;      /* columns of block_table                                    */
+  int32_t num_splits;              /* 0 = heuristic                                             */
+  void* workspace;
+  size_t workspace_bytes;
+} FaKvcacheParams;
+
+/* Split count fa_kvcache() will use for these parameters (resolves num_splits == 0). */
+int fa_kvcache_num_splits(const FaKvcacheParams* p);
+size_t fa_kvcache_workspace_bytes(const FaKvcacheParams* p);
+int fa_kvcache(const FaKvcacheParams* p, fa_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------- */
+/* Stand-alone log-sum-exp merge of split partials:                                             */
+/*   LSE = logsumexp_s lse_accum[s], O = sum_s exp(lse_accum[s] - LSE) * o_accum[s].            */
+/* Replaces kvcache_combine_kernel / kvcache_combine_kernel_legacy (kvcache_native.cu:676-780).  */
+/* Also the local step after the (O, LSE) exchange of a sequence-sharded forward.               */
+/* o_accum: (num_splits, rows, d) fp32; lse_accum: (num_splits, rows) fp32, -inf for an empty    */
+/* split; rows are ordered (b, h, seqlen_q).  Rows whose every split is empty get O=0, LSE=0.    */
+/* ------------------------------------------------------------------------------------------- */
+typedef struct FaCombineParams {
+  const float* o_accum;
+  const float* lse_accum;
+  void* o;          /* fp16 (b, seqlen_q, h, d) through the strides below                       */
+  float* lse;       /* (b, h, seqlen_q) contiguous, or NULL                                      */
+  int64_t o_batch_stride, o_row_stride, o_head_stride;
+  int32_t num_splits, b, h, seqlen_q, d;
+  int32_t reserved0;
+} FaCombineParams;
+
+int fa_combine(const FaCombineParams* p, fa_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H_ */
