@@ -85,11 +85,6 @@ struct Barriers {
   int abort_flag;
 };
 
-__device__ __forceinline__ bool wait_all(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
-  bool ok = mbar_wait(bar, parity, ctx);
-  return __all_sync(0xffffffffu, ok);
-}
-
 template <int D>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fwd_kernel(const __grid_constant__ FwdKernelParams p) {
@@ -306,7 +301,7 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
     bool ok = true;
 
     for (int j = 0; j < nbt; ++j) {
-      if (!(ok = wait_all(&bars->s_full[t], j & 1, ctx))) break;
+      if (!(ok = mbar_wait_warp(&bars->s_full[t], j & 1, ctx))) break;
       tc_fence_after_sync();
       uint32_t sr[4][32];
 #pragma unroll
@@ -393,7 +388,7 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
                 head * p.o_head_stride;
     }
     __half* orow = p.o + o_index;
-    if (ok && nbt > 0) ok = wait_all(&bars->o_full[t], 0, ctx);
+    if (ok && nbt > 0) ok = mbar_wait_warp(&bars->o_full[t], 0, ctx);
     if (ok && row0 + t * kBlockM < sq) {
       float lse_val = 0.f;
       float inv = 0.f;
