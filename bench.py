@@ -1,0 +1,376 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" = one forward + one backward pass of causal attention at the headline point of the metric:
+B=4, S_q=S_k=8192, H=32 query / 32 KV heads, D=128, fp16, seeded N(0,1) inputs (synthetic).  With N > 1
+(launched under torchrun, one rank per GPU) every rank runs the same independent (batch x head) shard
+-- weak scaling, no data-path collective -- and the reported value is the aggregate over ranks.
+
+Printed by rank 0: ONE JSON line with
+  value      TFLOP/s of the K timed steps, inputs resident in HBM, C-ABI calls with preallocated outputs
+  e2e        the same metric through the public API (flash_attn_func + autograd) with pinned HOST
+             inputs copied in and O, dQ, dK, dV copied out every step
+  roofline   the dominant kernel group of the step (backward: preprocess + dQ + dK/dV launches) against the
+             measured dense-GEMM peak; roofline_fwd and roofline_decode give the forward kernel and the
+             paged split-KV decode kernel (config: B=64, Hq=32, Hkv=8, D=128, L in [1024, 32768], page 256)
+  cpu_baseline  the fp32 CPU oracle timed on this box's host cores on a bounded sample of the same workload
+
+``--impl reference`` times the reference's attention math on the host CPU (the fp32 oracle port: the
+reference's CUDA extension needs an un-vendored CUTLASS tree and its Python math does not travel with
+this repository), each step a bounded sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOAD = dict(b=4, s=8192, h=32, h_k=32, d=128, causal=True)
+DECODE = dict(b=64, h=32, h_k=8, d=128, page=256, pages=16384, max_pages=129, lo=1024, hi=32768)
+METRIC = "attn fwd+bwd TFLOP/s (hd128 causal, S=8k)"
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
+
+
+def fwd_flops(b, h, sq, sk, d, causal):
+    f = 4.0 * b * h * sq * sk * d
+    return f * 0.5 if causal else f
+
+
+def load_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            data = json.loads(path.read_text())
+            return dict(hbm_gbs=float(data["hbm_gbs"]), bf16_tflops=float(data["bf16_tflops"]),
+                        bf16_tflops_sustained=float(data.get("bf16_tflops_sustained", data["bf16_tflops"]))), "measured"
+        except Exception:  # noqa: BLE001
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append(line.strip())
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1])); power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # clocks under load only: samples close to the maximum power seen
+        under = [c for c, p in zip(sm, power) if power and p >= 0.6 * max(power)] or sm
+        return {"sm_mhz": statistics.median(under) if under else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_attention_sample(slices: int, threads: int, s: int, d: int, causal: bool, seed: int = 1):
+    """fp32 oracle forward + backward on `slices` (batch, head) slices of the workload; returns seconds."""
+    import torch
+    from oracle import attention_oracle as orc
+
+    torch.set_num_threads(threads)
+    gen = torch.Generator().manual_seed(seed)
+    q, k, v, dout = (torch.randn(1, s, slices, d, generator=gen).half() for _ in range(4))
+    t0 = time.perf_counter()
+    orc.attention_forward(q, k, v, None, causal)
+    orc.attention_backward(q, k, v, dout, None, causal)
+    return time.perf_counter() - t0
+
+
+def run_reference(args, rank: int):
+    """CPU arm: the reference's fp32 attention math (oracle port) on the host cores, rank 0 only."""
+    if rank != 0:
+        return
+    w = WORKLOAD
+    threads = os.cpu_count() or 1
+    slices = 1
+    flops = 3.5 * fwd_flops(1, slices, w["s"], w["s"], w["d"], w["causal"])
+    for _ in range(args.warmup):
+        cpu_attention_sample(slices, threads, w["s"], w["d"], w["causal"])
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        cpu_attention_sample(slices, threads, w["s"], w["d"], w["causal"], seed=2 + i)
+    dt = time.perf_counter() - t0
+    value = flops * args.steps / dt / 1e12
+    sample = f"{slices} of {w['b'] * w['h']} (batch, head) slices per step, S={w['s']} D={w['d']} causal fwd+bwd"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 0, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "H8K: B4 S8192 H32 D128 causal fwd+bwd", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--skip-decode", action="store_true", help="skip the paged-decode measurement (needs 18 GB)")
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from flash_attention_turing_b200 import _ext, capi, flash_attn_func
+
+    ext = _ext.load()  # raises when the native library is missing: there is no fallback to measure
+    lib = capi.lib()
+    assert torch.cuda.is_available(), "bench.py needs a GPU for --impl ours"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks, peak_src = load_peaks()
+
+    w = WORKLOAD
+    b, s, h, hk, d, causal = w["b"], w["s"], w["h"], w["h_k"], w["d"], w["causal"]
+    scale = d ** -0.5
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+    q, k, v, dout = (torch.randn(b, s, n, d, device=dev, dtype=torch.half, generator=gen) for n in (h, hk, hk, h))
+    o = torch.empty_like(q)
+    lse = torch.empty(b, h, s, device=dev, dtype=torch.float32)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    fp = capi.fwd_params(q, k, v, o, lse, scale, causal)
+    bp = capi.bwd_params(q, k, v, o, dout, lse, dq, dk, dv, None, scale, causal)
+    ws = torch.empty(lib.fa_bwd_workspace_bytes(ctypes.byref(bp)), dtype=torch.uint8, device=dev)
+    bp = capi.bwd_params(q, k, v, o, dout, lse, dq, dk, dv, ws, scale, causal)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    f_fwd = fwd_flops(b, h, s, s, d, causal)
+    f_bwd = 2.5 * f_fwd
+
+    def step():
+        capi.check(lib.fa_fwd(ctypes.byref(fp), stream))
+        capi.check(lib.fa_bwd(ctypes.byref(bp), stream))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        x = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(x, op=dist.ReduceOp.MAX)
+        return float(x.item())
+
+    def timed(fn, iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1))
+
+    # ---- main timed region: W warm-up steps, then exactly K steps ----
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()  # runs through the warm-up, the timed region and the per-kernel timing loops
+    for _ in range(args.warmup):
+        step()
+    total_ms = timed(step, args.steps)
+    ms_per_step = total_ms / args.steps
+    value = (f_fwd + f_bwd) * world / (ms_per_step * 1e-3) / 1e12
+    status = lib.fa_device_status(1)
+
+    # ---- per-kernel durations (same inputs, after the main region) ----
+    reps = max(5, min(args.steps, 20))
+    fwd_ms = timed(lambda: capi.check(lib.fa_fwd(ctypes.byref(fp), stream)), reps) / reps
+    pre_ms = timed(lambda: capi.check(lib.fa_bwd_stages(ctypes.byref(bp), 1, stream)), reps) / reps
+    dq_ms = timed(lambda: capi.check(lib.fa_bwd_stages(ctypes.byref(bp), 2, stream)), reps) / reps
+    dkdv_ms = timed(lambda: capi.check(lib.fa_bwd_stages(ctypes.byref(bp), 4, stream)), reps) / reps
+    bwd_ms = pre_ms + dq_ms + dkdv_ms
+    clocks = sampler.stop() if rank == 0 else None
+    tensor_peak = peaks["bf16_tflops_sustained"]  # kernels timed inside a long loop under the power cap
+
+    def tensor_roofline(flops, ms, kernel):
+        ach = flops / (ms * 1e-3) / 1e12
+        return {"kernel": kernel, "bound": "tensor", "achieved": ach, "peak": tensor_peak, "unit": "TFLOP/s",
+                "frac": ach / tensor_peak, "frac_of_nominal_2250": ach / 2250.0, "traffic": None,
+                "peak_source": f"{peak_src} (cuBLAS bf16 sustained)", "ms_per_launch": ms}
+
+    roofline = tensor_roofline(f_bwd, bwd_ms, "backward: bwd_preprocess + bwd_dq_kernel + bwd_dkdv_kernel (2.5x forward FLOPs)")
+    roofline["ms_by_kernel"] = {"bwd_preprocess_kernel": pre_ms, "bwd_dq_kernel": dq_ms, "bwd_dkdv_kernel": dkdv_ms}
+    roofline_fwd = tensor_roofline(f_fwd, fwd_ms, "fwd_kernel<128>")
+
+    # ---- end to end through the public API, host buffers in and out every step ----
+    hq, hk_, hv, hdo = (x.cpu().pin_memory() for x in (q, k, v, dout))
+    ho, hdq, hdk, hdv = (torch.empty_like(x, device="cpu").pin_memory() for x in (q, q, k, v))
+
+    def e2e_step():
+        qd = hq.to(dev, non_blocking=True).requires_grad_(True)
+        kd = hk_.to(dev, non_blocking=True).requires_grad_(True)
+        vd = hv.to(dev, non_blocking=True).requires_grad_(True)
+        dd = hdo.to(dev, non_blocking=True)
+        out = flash_attn_func(qd, kd, vd, causal=causal)
+        gq, gk, gv = torch.autograd.grad(out, (qd, kd, vd), dd)
+        ho.copy_(out.detach(), non_blocking=True)
+        hdq.copy_(gq, non_blocking=True)
+        hdk.copy_(gk, non_blocking=True)
+        hdv.copy_(gv, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+    e2e_value = (f_fwd + f_bwd) * world / (e2e_ms * 1e-3) / 1e12
+    h2d = sum(x.numel() * 2 for x in (q, k, v, dout))
+    d2h = sum(x.numel() * 2 for x in (q, q, k, v))
+    del hq, hk_, hv, hdo, ho, hdq, hdk, hdv
+
+    # ---- paged split-KV decode (HBM-bound), kernel path through the C ABI ----
+    decode = None
+    roofline_decode = None
+    if not args.skip_decode:
+        del q, k, v, dout, o, dq, dk, dv
+        torch.cuda.empty_cache()
+        c = DECODE
+        gen_c = torch.Generator().manual_seed(1004)
+        lens = torch.randint(c["lo"], c["hi"], (c["b"],), generator=gen_c, dtype=torch.int32)
+        perm = torch.randperm(c["pages"], generator=gen_c).to(torch.int32)
+        table = torch.zeros(c["b"], c["max_pages"], dtype=torch.int32)
+        off = 0
+        for i in range(c["b"]):
+            n = (int(lens[i]) + 1 + c["page"] - 1) // c["page"]
+            table[i, :n] = perm[off:off + n]
+            off += n
+        kc = torch.randn(c["pages"], c["page"], c["h_k"], c["d"], device=dev, dtype=torch.half, generator=gen)
+        vc = torch.randn(c["pages"], c["page"], c["h_k"], c["d"], device=dev, dtype=torch.half, generator=gen)
+        q1 = torch.randn(c["b"], 1, c["h"], c["d"], device=dev, dtype=torch.half, generator=gen)
+        kn = torch.randn(c["b"], 1, c["h_k"], c["d"], device=dev, dtype=torch.half, generator=gen)
+        vn = torch.randn(c["b"], 1, c["h_k"], c["d"], device=dev, dtype=torch.half, generator=gen)
+        o1 = torch.empty_like(q1)
+        lse1 = torch.empty(c["b"], c["h"], 1, device=dev, dtype=torch.float32)
+        lens_d, table_d = lens.to(dev), table.to(dev)
+        kv_bytes = float((lens.double() + 1).sum()) * 2 * c["h_k"] * c["d"] * 2
+        alg_bytes = (kv_bytes + 2 * c["b"] * c["h"] * c["d"] * 2 + 2 * 2 * c["b"] * c["h_k"] * c["d"] * 2 +
+                     4 * (c["b"] + float(((lens + 1 + c["page"] - 1) // c["page"]).sum())) + 4 * c["b"] * c["h"])
+        decode = {"metric": "paged split-KV decode HBM GB/s", "unit": "GB/s", "algorithmic_bytes": alg_bytes,
+                  "config": "B64 Hq32 Hkv8 D128 L~U[1024,32768] page256 pool 16384 pages", "by_num_splits": {}}
+        best = None
+        for splits in (1, 4, 16, 0):
+            kp = capi.kvcache_params(q1, kc, vc, kn, vn, o1, lse1, lens_d, table_d, c["d"] ** -0.5, True, splits)
+            need = lib.fa_kvcache_workspace_bytes(ctypes.byref(kp))
+            wsk = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+            kp.workspace, kp.workspace_bytes = wsk.data_ptr(), need
+            fn = lambda: capi.check(lib.fa_kvcache(ctypes.byref(kp), stream))  # noqa: E731
+            for _ in range(3):
+                fn()
+            ms = timed(fn, 20) / 20
+            gbs = alg_bytes * world / (ms * 1e-3) / 1e9
+            decode["by_num_splits"][str(splits)] = {"ms": ms, "gbs": gbs,
+                                                    "effective_splits": lib.fa_kvcache_num_splits(ctypes.byref(kp))}
+            if best is None or gbs > best[1]:
+                best = (splits, gbs, ms)
+        decode["value"] = best[1]
+        per_gpu = best[1] / world
+        roofline_decode = {"kernel": "decode_kernel<128> + combine_kernel<128> + append_kernel", "bound": "hbm",
+                           "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": per_gpu / peaks["hbm_gbs"],
+                           "frac_of_nominal_8000": per_gpu / 8000.0, "traffic": None, "num_splits": best[0],
+                           "peak_source": f"{peak_src} (copy bandwidth)", "ms_per_launch": best[2]}
+        status |= lib.fa_device_status(1)
+        del kc, vc
+
+    # ---- CPU baseline: fp32 oracle on the host cores, bounded sample, rank 0 only ----
+    cpu_baseline = None
+    if rank == 0 and not args.skip_cpu_baseline:
+        threads = os.cpu_count() or 1
+        slices = 4
+        cpu_attention_sample(1, threads, 2048, d, causal)  # warm the thread pool
+        sec = cpu_attention_sample(slices, threads, s, d, causal)
+        reps_cpu = 1
+        while sec < 10.0 and reps_cpu < 6:
+            sec += cpu_attention_sample(slices, threads, s, d, causal, seed=10 + reps_cpu)
+            reps_cpu += 1
+        cpu_flops = 3.5 * fwd_flops(1, slices, s, s, d, causal) * reps_cpu
+        cpu_baseline = {"value": cpu_flops / sec / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                        "sample": f"{slices * reps_cpu} of {b * h} (batch, head) slices of the workload "
+                                  f"(S={s}, D={d}, causal, fwd+bwd), fp32 torch oracle, {sec:.1f} s"}
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "H8K: B4 S8192 Hq32 Hkv32 D128 causal, forward + backward, per GPU",
+                       "sharding": "independent (batch x head) shards per GPU, no collective",
+                       "l2": "inputs_larger_than_l2 (q,k,v,dO,O = 5 x 268 MB vs 126 MB L2)"},
+            "fwd_tflops": f_fwd / (fwd_ms * 1e-3) / 1e12, "bwd_tflops": f_bwd / (bwd_ms * 1e-3) / 1e12,
+            "roofline": roofline, "roofline_fwd": roofline_fwd, "roofline_decode": roofline_decode,
+            "decode": decode, "cpu_baseline": cpu_baseline,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "path": "flash_attn_func + torch.autograd.grad, pinned host q,k,v,dO in; O,dQ,dK,dV out"},
+            "gpu_launches": 4 * args.steps, "clocks": clocks, "device_status": status,
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -18,6 +18,7 @@ EXPORTED_SYMBOLS = (
     "fa_fwd",
     "fa_bwd_workspace_bytes",
     "fa_bwd",
+    "fa_bwd_stages",
     "fa_kvcache_num_splits",
     "fa_kvcache_workspace_bytes",
     "fa_kvcache",
@@ -101,6 +102,8 @@ def lib() -> C.CDLL:
             fn = getattr(l, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(struct), _vp]
+        l.fa_bwd_stages.restype = C.c_int
+        l.fa_bwd_stages.argtypes = [C.POINTER(FaBwdParams), C.c_int, _vp]
         l.fa_bwd_workspace_bytes.restype = _sz
         l.fa_bwd_workspace_bytes.argtypes = [C.POINTER(FaBwdParams)]
         l.fa_kvcache_workspace_bytes.restype = _sz
@@ -114,3 +117,67 @@ def lib() -> C.CDLL:
 def check(rc: int) -> None:
     if rc != 0:
         raise FaError(rc, lib().fa_last_error().decode())
+
+
+# ------------------------------------------------------------------------------------------------
+# helpers that fill the parameter structs from torch tensors (dense layouts); tests and the benchmark
+# use them to call the C ABI with preallocated outputs
+# ------------------------------------------------------------------------------------------------
+def _set_strides(p, name, x):
+    setattr(p, f"{name}_batch_stride", x.stride(0))
+    setattr(p, f"{name}_row_stride", x.stride(1))
+    setattr(p, f"{name}_head_stride", x.stride(2))
+
+
+def fwd_params(q, k, v, o, lse, softmax_scale: float, causal: bool) -> FaFwdParams:
+    """q (b, sq, h, d), k/v (b, sk, hk, d), o like q, lse (b, h, sq) fp32 -- all CUDA tensors."""
+    p = FaFwdParams()
+    p.q, p.k, p.v, p.o, p.lse = (x.data_ptr() for x in (q, k, v, o, lse))
+    for name, x in (("q", q), ("k", k), ("v", v), ("o", o)):
+        _set_strides(p, name, x)
+    p.lse_row_stride = lse.shape[2]
+    p.b, p.seqlen_q, p.h, p.d = q.shape
+    p.seqlen_k, p.h_k, p.k_batch = k.shape[1], k.shape[2], k.shape[0]
+    p.softmax_scale, p.is_causal = softmax_scale, int(causal)
+    return p
+
+
+def bwd_params(q, k, v, o, dout, lse, dq, dk, dv, workspace, softmax_scale: float, causal: bool) -> FaBwdParams:
+    p = FaBwdParams()
+    p.q, p.k, p.v, p.o, p.dout, p.lse, p.dq, p.dk, p.dv = (x.data_ptr() for x in (q, k, v, o, dout, lse, dq, dk, dv))
+    for name, x in (("q", q), ("k", k), ("v", v), ("o", o), ("do", dout), ("dq", dq), ("dk", dk), ("dv", dv)):
+        _set_strides(p, name, x)
+    p.lse_row_stride = lse.shape[2]
+    p.b, p.seqlen_q, p.h, p.d = q.shape
+    p.seqlen_k, p.h_k = k.shape[1], k.shape[2]
+    p.softmax_scale, p.is_causal = softmax_scale, int(causal)
+    if workspace is not None:
+        p.workspace, p.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    return p
+
+
+def kvcache_params(q, k_cache, v_cache, k_new, v_new, o, lse, cache_seqlens, block_table, softmax_scale: float,
+                   causal: bool, num_splits: int, cache_batch_idx=None) -> FaKvcacheParams:
+    p = FaKvcacheParams()
+    p.q, p.k_cache, p.v_cache, p.o, p.lse = (x.data_ptr() for x in (q, k_cache, v_cache, o, lse))
+    for name, x in (("q", q), ("kc", k_cache), ("vc", v_cache), ("o", o)):
+        _set_strides(p, name, x)
+    p.seqlen_new = 0
+    if k_new is not None:
+        p.k_new, p.v_new = k_new.data_ptr(), v_new.data_ptr()
+        _set_strides(p, "kn", k_new)
+        _set_strides(p, "vn", v_new)
+        p.seqlen_new = k_new.shape[1]
+    p.b, p.seqlen_q, p.h, p.d = q.shape
+    p.h_k = k_cache.shape[2]
+    p.cache_batch, p.seqlen_cache = k_cache.shape[0], k_cache.shape[1]
+    p.softmax_scale, p.is_causal = softmax_scale, int(causal)
+    p.cache_seqlens = cache_seqlens.data_ptr()
+    if cache_batch_idx is not None:
+        p.cache_batch_idx = cache_batch_idx.data_ptr()
+    if block_table is not None:
+        p.block_table = block_table.data_ptr()
+        p.block_table_batch_stride = block_table.stride(0)
+        p.max_blocks_per_seq = block_table.shape[1]
+    p.num_splits = num_splits
+    return p

@@ -131,6 +131,14 @@ typedef struct FaBwdParams {
 size_t fa_bwd_workspace_bytes(const FaBwdParams* p);
 int fa_bwd(const FaBwdParams* p, fa_stream_t stream);
 
+/* Runs a subset of the three kernels of fa_bwd(): stage_mask bit 0 = preprocess (rowsum(dO*O), LSE in
+ * base-2 units -> workspace), bit 1 = dQ kernel, bit 2 = dK/dV kernel.  fa_bwd(p, s) is
+ * fa_bwd_stages(p, 7, s).  For timing one kernel at a time with CUDA events around the call (the
+ * reference launches its three kernels back to back in run_flash_bwd,
+ * src/flash_bwd_launch_template.h:84-138, and offers no such hook); bits 1 and 2 need a workspace that
+ * an earlier call with bit 0 filled for the same inputs. */
+int fa_bwd_stages(const FaBwdParams* p, int stage_mask, fa_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------- */
 /* KV-cache step: append k_new/v_new in place at cache_seqlens, then attend q against            */
 /* [0, cache_seqlens + seqlen_new) with split-KV and the LSE combine.                           */

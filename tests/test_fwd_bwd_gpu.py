@@ -1,0 +1,257 @@
+"""GPU parity of the forward and backward kernels against the CPU fp32 oracle, through the torch
+binding (which calls the C ABI).  Shapes follow the reference's grid (test_flash_attn.py:51-140 of
+Cy-47/flash-attention-turing: odd lengths, Sq != Sk both ways, GQA/MQA head pairs, both head dims,
+causal on/off, explicit scale) plus MHA cases for the packed variants, which the reference's grid
+never reaches (all of its head pairs have Hq != Hk)."""
+import pytest
+import torch
+
+from helpers import (LSE_TOL, MAX_ABS_TOL, MEAN_ABS_TOL, emulated_reference_kernel_error, err_stats, load_golden,
+                     randn_half, t)
+from oracle import attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+SEQ_PAIRS = [(1, 1), (2, 2), (63, 65), (65, 63), (127, 129), (128, 128), (129, 257), (257, 129), (113, 203),
+             (256, 512), (512, 256), (384, 384), (897, 1024), (1025, 1023), (1, 239), (239, 1), (799, 3), (3, 799)]
+HEAD_PAIRS = [(2, 1), (4, 2), (6, 3), (6, 1), (4, 4)]
+
+
+def _inputs(seed, b, sq, sk, h, hk, d):
+    gen = torch.Generator().manual_seed(seed)
+    return (randn_half(gen, b, sq, h, d), randn_half(gen, b, sk, hk, d), randn_half(gen, b, sk, hk, d),
+            randn_half(gen, b, sq, h, d))
+
+
+def _check(name, got, want, max_tol=MAX_ABS_TOL, mean_tol=MEAN_ABS_TOL):
+    """The reference's bounds are stated between two fp16 results; against the fp32 oracle an allowance
+    is added for the two fp16 roundings every such kernel has (the reference's included,
+    flash_fwd_kernel.h:578 and flash_bwd_kernel.h:439): P / dS before the second GEMM and the output
+    itself, half an ulp (2^-11 relative) each."""
+    mx, mean = err_stats(got, want)
+    wf = want.detach().float().abs()
+    if wf.numel():
+        max_tol = max_tol + 2.0 ** -10 * wf.max().item()
+        mean_tol = mean_tol + 2.0 ** -10 * wf.mean().item()
+    assert not torch.isnan(got).any(), f"{name}: NaN"
+    assert mx <= max_tol, f"{name}: max abs err {mx:.3e} > {max_tol:.1e}"
+    assert mean <= mean_tol, f"{name}: mean abs err {mean:.3e} > {mean_tol:.1e}"
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("sq,sk", SEQ_PAIRS)
+def test_dense_forward_backward_grid(ext, d, causal, sq, sk):
+    from flash_attention_turing_b200 import flash_attn_func
+
+    idx = SEQ_PAIRS.index((sq, sk))
+    h, hk = HEAD_PAIRS[idx % len(HEAD_PAIRS)]
+    b = 1 + idx % 3
+    scale = None if idx % 2 == 0 else 0.3
+    q, k, v, dout = _inputs(100 + idx, b, sq, sk, h, hk, d)
+    qd, kd, vd = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    out = flash_attn_func(qd, kd, vd, softmax_scale=scale, causal=causal)
+    dq, dk, dv = torch.autograd.grad(out, (qd, kd, vd), dout.to(DEV))
+    s = d ** -0.5 if scale is None else scale
+    o_ref, _ = orc.attention_forward(q, k, v, s, causal)
+    rq, rk, rv = orc.attention_backward(q, k, v, dout, s, causal)
+    _check("O", out, o_ref)
+    _check("dQ", dq, rq)
+    _check("dK", dk, rk)
+    _check("dV", dv, rv)
+
+
+@pytest.mark.parametrize("d,b,s,h,hk,causal", [(64, 2, 512, 8, 8, False), (128, 1, 1024, 4, 1, True)])
+def test_forward_error_within_twice_the_reference_kernels(ext, d, b, s, h, hk, causal):
+    # C1 of the benchmark configs (B2 S512 H8 D64 non-causal) and a causal GQA case: O within 2x the
+    # error of an emulation of the reference kernel's rounding points, LSE within 1e-3.
+    q, k, v, _ = _inputs(1001, b, s, s, h, hk, d)
+    out, lse = ext.fwd(q.to(DEV), k.to(DEV), v.to(DEV), d ** -0.5, causal)
+    o_ref, lse_ref = orc.attention_forward(q, k, v, None, causal)
+    ref_err = emulated_reference_kernel_error(q, k, v, d ** -0.5, causal, o_ref)
+    mx, _ = err_stats(out, o_ref)
+    assert mx <= 2 * ref_err + 1e-5, f"O err {mx:.3e} vs reference-kernel emulation {ref_err:.3e}"
+    assert err_stats(lse, lse_ref)[0] <= LSE_TOL
+
+
+@pytest.mark.parametrize("name", ["fwd_d64_noncausal", "fwd_d64_causal", "fwd_d128_causal_gqa", "fwd_d128_sq_gt_sk"])
+def test_golden_fixtures(ext, name):
+    # fixtures hold outputs of the reference's own Python math; keys beyond lens[b] are cut per sequence
+    g = load_golden(name)
+    q, k, v, dout = (t(g[x]) for x in ("q", "k", "v", "dout"))
+    lens = g["lens"].tolist()
+    scale, causal = float(g["scale"]), bool(g["causal"])
+    for b in range(q.shape[0]):
+        qb, kb, vb = q[b:b + 1].to(DEV), k[b:b + 1, : lens[b]].contiguous().to(DEV), v[b:b + 1, : lens[b]].contiguous().to(DEV)
+        out, lse = ext.fwd(qb, kb, vb, scale, causal)
+        dq, dk, dv = ext.bwd(qb, kb, vb, out, lse, dout[b:b + 1].to(DEV), scale, causal)
+        want_out = torch.nan_to_num(t(g["out"])[b:b + 1], nan=0.0)
+        want_lse = t(g["lse"])[b:b + 1]
+        want_lse = torch.where(torch.isfinite(want_lse), want_lse, torch.zeros_like(want_lse))
+        _check("O", out, want_out)
+        assert err_stats(lse, want_lse)[0] <= LSE_TOL
+        _check("dQ", dq, t(g["dq"])[b:b + 1])
+        _check("dK", dk, t(g["dk"])[b:b + 1, : lens[b]])
+        _check("dV", dv, t(g["dv"])[b:b + 1, : lens[b]])
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_packed_variants_match_unpacked(ext, d, causal):
+    from flash_attention_turing_b200 import flash_attn_func, flash_attn_kvpacked_func, flash_attn_qkvpacked_func
+
+    b, s, h = 2, 200, 4
+    gen = torch.Generator().manual_seed(7 + d)
+    qkv = randn_half(gen, b, s, 3, h, d).to(DEV).requires_grad_(True)
+    dout = randn_half(gen, b, s, h, d).to(DEV)
+    out_p = flash_attn_qkvpacked_func(qkv, causal=causal)
+    (dqkv,) = torch.autograd.grad(out_p, qkv, dout)
+    q, k, v = (qkv.detach()[:, :, i].contiguous().requires_grad_(True) for i in range(3))
+    out = flash_attn_func(q, k, v, causal=causal)
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), dout)
+    assert torch.equal(out_p, out)  # same kernel, same data, strided vs contiguous: bit-identical
+    assert torch.equal(dqkv[:, :, 0], dq) and torch.equal(dqkv[:, :, 1], dk) and torch.equal(dqkv[:, :, 2], dv)
+    o_ref, _ = orc.attention_forward(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), None, causal)
+    _check("O", out_p, o_ref)
+
+    hk = 2
+    kv = randn_half(gen, b, s, 2, hk, d).to(DEV).requires_grad_(True)
+    q2 = q.detach().clone().requires_grad_(True)
+    out_kv = flash_attn_kvpacked_func(q2, kv, causal=causal)
+    dq2, dkv = torch.autograd.grad(out_kv, (q2, kv), dout)
+    k2, v2 = (kv.detach()[:, :, i].contiguous().requires_grad_(True) for i in range(2))
+    q3 = q.detach().clone().requires_grad_(True)
+    out3 = flash_attn_func(q3, k2, v2, causal=causal)
+    dq3, dk3, dv3 = torch.autograd.grad(out3, (q3, k2, v2), dout)
+    assert torch.equal(out_kv, out3) and torch.equal(dq2, dq3)
+    assert torch.equal(dkv[:, :, 0], dk3) and torch.equal(dkv[:, :, 1], dv3)
+
+
+def _varlen_case(seed, lens_q, lens_k, h, hk, d):
+    gen = torch.Generator().manual_seed(seed)
+    cq = torch.tensor([0] + torch.tensor(lens_q).cumsum(0).tolist(), dtype=torch.int32)
+    ck = torch.tensor([0] + torch.tensor(lens_k).cumsum(0).tolist(), dtype=torch.int32)
+    tq, tk = int(cq[-1]), int(ck[-1])
+    return (randn_half(gen, tq, h, d), randn_half(gen, tk, hk, d), randn_half(gen, tk, hk, d),
+            randn_half(gen, tq, h, d), cq, ck)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("lens_q,lens_k,h,hk", [
+    ([100, 300, 57], [100, 300, 57], 4, 2),
+    ([128, 1, 513, 64], [200, 64, 513, 1], 2, 1),
+    ([1, 2, 3, 129, 255], [7, 2, 300, 129, 1], 6, 3),
+    ([640], [640], 4, 4),
+])
+def test_varlen_forward_backward(ext, d, causal, lens_q, lens_k, h, hk):
+    from flash_attention_turing_b200 import flash_attn_varlen_func
+
+    q, k, v, dout, cq, ck = _varlen_case(31 + d, lens_q, lens_k, h, hk, d)
+    qd, kd, vd = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    out = flash_attn_varlen_func(qd, kd, vd, cq.to(DEV), ck.to(DEV), max(lens_q), max(lens_k), causal=causal)
+    dq, dk, dv = torch.autograd.grad(out, (qd, kd, vd), dout.to(DEV))
+    o_ref, lses = orc.varlen_forward(q, k, v, cq, ck, None, causal)
+    rq, rk, rv = orc.varlen_backward(q, k, v, dout, cq, ck, None, causal)
+    _check("O", out, o_ref)
+    _check("dQ", dq, rq)
+    _check("dK", dk, rk)
+    _check("dV", dv, rv)
+    # padded LSE (b, h, max_seqlen_q): valid part matches, padding stays zero
+    _, lse = ext.varlen_fwd(qd.detach(), kd.detach(), vd.detach(), cq.to(DEV), ck.to(DEV), max(lens_q), max(lens_k),
+                            d ** -0.5, causal)
+    for i, l in enumerate(lses):
+        assert err_stats(lse[i, :, : lens_q[i]], l)[0] <= LSE_TOL
+        assert lse[i, :, lens_q[i]:].abs().max().item() == 0 if lens_q[i] < max(lens_q) else True
+
+
+def test_varlen_packed_variants(ext):
+    from flash_attention_turing_b200 import (flash_attn_varlen_func, flash_attn_varlen_kvpacked_func,
+                                             flash_attn_varlen_qkvpacked_func)
+
+    lens = [90, 257, 33]
+    d, h = 128, 4
+    gen = torch.Generator().manual_seed(5)
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32).to(DEV)
+    total = sum(lens)
+    qkv = randn_half(gen, total, 3, h, d).to(DEV).requires_grad_(True)
+    dout = randn_half(gen, total, h, d).to(DEV)
+    out_p = flash_attn_varlen_qkvpacked_func(qkv, cu, max(lens), causal=True)
+    (dqkv,) = torch.autograd.grad(out_p, qkv, dout)
+    q, k, v = (qkv.detach()[:, i].contiguous().requires_grad_(True) for i in range(3))
+    out = flash_attn_varlen_func(q, k, v, cu, cu, max(lens), max(lens), causal=True)
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), dout)
+    assert torch.equal(out_p, out)
+    assert torch.equal(dqkv[:, 0], dq) and torch.equal(dqkv[:, 1], dk) and torch.equal(dqkv[:, 2], dv)
+    kv = torch.stack((k.detach(), v.detach()), dim=1).requires_grad_(True)
+    q2 = q.detach().clone().requires_grad_(True)
+    out_kv = flash_attn_varlen_kvpacked_func(q2, kv, cu, cu, max(lens), max(lens), causal=True)
+    dq2, dkv = torch.autograd.grad(out_kv, (q2, kv), dout)
+    assert torch.equal(out_kv, out) and torch.equal(dq2, dq) and torch.equal(dkv[:, 0], dk) and torch.equal(dkv[:, 1], dv)
+
+
+def test_run_to_run_determinism(ext):
+    # every accumulation order is fixed (no atomics): repeated launches are bit-identical, which also
+    # catches races on shared memory / TMEM
+    q, k, v, dout = _inputs(77, 2, 700, 700, 4, 2, 128)
+    qd, kd, vd, dd = (x.to(DEV) for x in (q, k, v, dout))
+    first = None
+    for _ in range(3):
+        out, lse = ext.fwd(qd, kd, vd, 128 ** -0.5, True)
+        grads = ext.bwd(qd, kd, vd, out, lse, dd, 128 ** -0.5, True)
+        cur = [out, lse, *grads]
+        if first is None:
+            first = [x.clone() for x in cur]
+        else:
+            assert all(torch.equal(a, b) for a, b in zip(first, cur))
+
+
+def test_no_grad_and_requires_grad_flags(ext):
+    from flash_attention_turing_b200 import flash_attn_func
+
+    q, k, v, _ = _inputs(3, 1, 64, 64, 2, 2, 64)
+    with torch.no_grad():
+        out = flash_attn_func(q.to(DEV), k.to(DEV), v.to(DEV))
+    assert not out.requires_grad
+    qd = q.to(DEV).requires_grad_(True)
+    out = flash_attn_func(qd, k.to(DEV), v.to(DEV), causal=True)
+    (dq,) = torch.autograd.grad(out.float().sum(), qd)
+    assert dq.shape == qd.shape and dq.dtype == torch.float16
+
+
+def test_binding_errors(ext):
+    q = torch.randn(1, 8, 4, 96, device=DEV, dtype=torch.half)
+    with pytest.raises(RuntimeError, match="head_dim 64 or 128"):
+        ext.fwd(q, q, q, 1.0, False)
+    q = torch.randn(1, 8, 4, 64, device=DEV, dtype=torch.half)
+    k = torch.randn(1, 8, 3, 64, device=DEV, dtype=torch.half)
+    with pytest.raises(RuntimeError, match="divisible by num_heads_k"):
+        ext.fwd(q, k, k, 1.0, False)
+    with pytest.raises(RuntimeError, match="rank-4"):
+        ext.fwd(q[0], k[0], k[0], 1.0, False)
+
+
+@pytest.mark.parametrize("causal", [True])
+def test_full_size_causal_config_by_sampling(ext, causal):
+    # C2 of the benchmark configs: B4 S4096 H32 D128 causal, forward + backward at full size.
+    # The fp32 oracle is evaluated on two (batch, head) slices; attention is independent per
+    # (batch, head), so a slice of the full-size launch must match the oracle of that slice.
+    b, s, h, d = 4, 4096, 32, 128
+    gen = torch.Generator(device=DEV).manual_seed(1002)
+    q, k, v, dout = (torch.randn(b, s, h, d, device=DEV, dtype=torch.half, generator=gen) for _ in range(4))
+    out, lse = ext.fwd(q, k, v, d ** -0.5, causal)
+    dq, dk, dv = ext.bwd(q, k, v, out, lse, dout, d ** -0.5, causal)
+    for bi, hi in [(0, 0), (3, 17)]:
+        sl = lambda x: x[bi:bi + 1, :, hi:hi + 1].cpu()  # noqa: E731
+        o_ref, lse_ref = orc.attention_forward(sl(q), sl(k), sl(v), None, causal)
+        rq, rk, rv = orc.attention_backward(sl(q), sl(k), sl(v), sl(dout), None, causal)
+        _check("O", sl(out), o_ref)
+        assert err_stats(lse[bi:bi + 1, hi:hi + 1], lse_ref)[0] <= LSE_TOL
+        _check("dQ", sl(dq), rq)
+        _check("dK", sl(dk), rk, max_tol=2 * MAX_ABS_TOL)  # grows with the number of summed rows
+        _check("dV", sl(dv), rv, max_tol=2 * MAX_ABS_TOL)
+    # size-independent property: every softmax row sums to one => with V = 1, O = 1 exactly
+    ones = torch.ones_like(v)
+    o1, _ = ext.fwd(q, k, ones, d ** -0.5, causal)
+    assert (o1.float() - 1).abs().max().item() <= 2e-3
