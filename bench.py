@@ -153,6 +153,64 @@ def run_reference(args, rank: int):
     }), flush=True)
 
 
+def run_profile_case(args):
+    """Reduced cases for profiler captures (a few hundred MB on the device, inputs still larger than L2):
+    fwd / bwd: B2 S4096 H16 D128 causal; decode: B16 Hq32 Hkv8 D128, L ~ U[1024, 32768], 4096-page pool."""
+    import torch
+
+    from flash_attention_turing_b200 import _ext, capi
+
+    _ext.load()
+    lib = capi.lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    gen = torch.Generator(device=dev).manual_seed(5)
+    if args.profile in ("fwd", "bwd"):
+        b, s, h, d = 2, 4096, 16, 128
+        q, k, v, dout = (torch.randn(b, s, h, d, device=dev, dtype=torch.half, generator=gen) for _ in range(4))
+        o, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+        lse = torch.empty(b, h, s, device=dev, dtype=torch.float32)
+        fp = capi.fwd_params(q, k, v, o, lse, d ** -0.5, True)
+        bp = capi.bwd_params(q, k, v, o, dout, lse, dq, dk, dv, None, d ** -0.5, True)
+        ws = torch.empty(lib.fa_bwd_workspace_bytes(ctypes.byref(bp)), dtype=torch.uint8, device=dev)
+        bp = capi.bwd_params(q, k, v, o, dout, lse, dq, dk, dv, ws, d ** -0.5, True)
+        capi.check(lib.fa_fwd(ctypes.byref(fp), stream))
+        for _ in range(args.profile_iters):
+            if args.profile == "fwd":
+                capi.check(lib.fa_fwd(ctypes.byref(fp), stream))
+            else:
+                capi.check(lib.fa_bwd(ctypes.byref(bp), stream))
+    else:
+        bb, hq, hk, d, page, pages, max_pages = 16, 32, 8, 128, 256, 4096, 129
+        gen_c = torch.Generator().manual_seed(1004)
+        lens = torch.randint(1024, 32768, (bb,), generator=gen_c, dtype=torch.int32)
+        perm = torch.randperm(pages, generator=gen_c).to(torch.int32)
+        table = torch.zeros(bb, max_pages, dtype=torch.int32)
+        off = 0
+        for i in range(bb):
+            n = (int(lens[i]) + 1 + page - 1) // page
+            table[i, :n] = perm[off:off + n]
+            off += n
+        kc = torch.randn(pages, page, hk, d, device=dev, dtype=torch.half, generator=gen)
+        vc = torch.randn(pages, page, hk, d, device=dev, dtype=torch.half, generator=gen)
+        q1 = torch.randn(bb, 1, hq, d, device=dev, dtype=torch.half, generator=gen)
+        kn = torch.randn(bb, 1, hk, d, device=dev, dtype=torch.half, generator=gen)
+        vn = torch.randn(bb, 1, hk, d, device=dev, dtype=torch.half, generator=gen)
+        o1 = torch.empty_like(q1)
+        lse1 = torch.empty(bb, hq, 1, device=dev, dtype=torch.float32)
+        kp = capi.kvcache_params(q1, kc, vc, kn, vn, o1, lse1, lens.to(dev), table.to(dev), d ** -0.5, True, 4)
+        need = lib.fa_kvcache_workspace_bytes(ctypes.byref(kp))
+        wsk = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+        kp.workspace, kp.workspace_bytes = wsk.data_ptr(), need
+        for _ in range(args.profile_iters):
+            capi.check(lib.fa_kvcache(ctypes.byref(kp), stream))
+        kv_bytes = float((lens.double() + 1).sum()) * 2 * hk * d * 2
+        print(json.dumps({"profile": "decode", "kv_bytes_per_launch": kv_bytes}))
+    torch.cuda.synchronize()
+    print(json.dumps({"profile": args.profile, "device_status": lib.fa_device_status(1)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -161,7 +219,13 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--skip-decode", action="store_true", help="skip the paged-decode measurement (needs 18 GB)")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", choices=["fwd", "bwd", "decode"], default=None,
+                    help="run a few launches of one kernel group on a reduced case and exit (for ncu captures)")
+    ap.add_argument("--profile-iters", type=int, default=3)
     args = ap.parse_args()
+    if args.profile:
+        run_profile_case(args)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))
