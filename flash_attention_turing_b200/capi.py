@@ -22,6 +22,7 @@ EXPORTED_SYMBOLS = (
     "fa_kvcache_num_splits",
     "fa_kvcache_workspace_bytes",
     "fa_kvcache",
+    "fa_kvcache_noalloc",
     "fa_combine",
 )
 
@@ -97,8 +98,8 @@ def lib() -> C.CDLL:
         l.fa_abi_version.restype = C.c_int
         l.fa_device_status.restype = C.c_int
         l.fa_device_status.argtypes = [C.c_int]
-        for name, struct in (("fa_fwd", FaFwdParams), ("fa_bwd", FaBwdParams),
-                             ("fa_kvcache", FaKvcacheParams), ("fa_combine", FaCombineParams)):
+        for name, struct in (("fa_fwd", FaFwdParams), ("fa_bwd", FaBwdParams), ("fa_kvcache", FaKvcacheParams),
+                             ("fa_kvcache_noalloc", FaKvcacheParams), ("fa_combine", FaCombineParams)):
             fn = getattr(l, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(struct), _vp]

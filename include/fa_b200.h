@@ -185,6 +185,30 @@ int fa_kvcache_num_splits(const FaKvcacheParams* p);
 size_t fa_kvcache_workspace_bytes(const FaKvcacheParams* p);
 int fa_kvcache(const FaKvcacheParams* p, fa_stream_t stream);
 
+/* KV-cache step for hosts that cannot allocate device memory.  No counterpart in the reference.   */
+/*                                                                                             */
+/* Some callers of this library have no allocator to hand the split-KV scratch from: a serving    */
+/* loop whose memory pool was sized and frozen at start-up, a plugin running inside another       */
+/* runtime's stream callback or graph node where cudaMalloc is forbidden, a host written in a     */
+/* language binding that exposes launches but not allocation.  fa_kvcache_noalloc() does what      */
+/* fa_kvcache() does, with identical kernels and results, but takes the partial (O, LSE) scratch   */
+/* from an array that is part of the library image itself; p->workspace and p->workspace_bytes are */
+/* ignored.  It calls no cudaMalloc / cudaFree and no allocating library routine.                 */
+/*                                                                                             */
+/* Limit: the array is FA_KVCACHE_NOALLOC_SCRATCH_BYTES (32 MiB) per GPU, held by every GPU that  */
+/* loads the library until the process exits.  A call that needs more -- i.e. whose               */
+/* fa_kvcache_workspace_bytes() exceeds that -- is rejected with FA_ERR_WORKSPACE and nothing is  */
+/* launched (use fewer splits, or fa_kvcache() with your own buffer).                             */
+/* First call on a device: the library looks up the device address of the array (one              */
+/* cudaGetSymbolAddress with that device current) and caches it; make this first call outside any */
+/* stream capture.                                                                             */
+/* Sharing: every call on a GPU uses the same array.  The kernels overwrite every element they     */
+/* later read, so no clearing is needed between calls, but two calls that can overlap on the GPU   */
+/* (different streams without an ordering between them) race on it: serialise them.               */
+/* ------------------------------------------------------------------------------------------- */
+#define FA_KVCACHE_NOALLOC_SCRATCH_BYTES (32u * 1024u * 1024u)
+int fa_kvcache_noalloc(const FaKvcacheParams* p, fa_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------- */
 /* Stand-alone log-sum-exp merge of split partials:                                             */
 /*   LSE = logsumexp_s lse_accum[s], O = sum_s exp(lse_accum[s] - LSE) * o_accum[s].            */
