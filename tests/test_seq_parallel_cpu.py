@@ -1,0 +1,83 @@
+"""World-size-2 (and 4) gloo tests of the sequence-sharded forward's exchange logic on CPU ranks.
+
+The kernels are injected: the CPU oracle stands in for the forward kernel and for the combine kernel,
+so what is tested here is the sharding arithmetic (causal offsets per shard), the all-to-all layout and
+the merge -- not any CPU execution path of the product (there is none)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import attention_oracle as orc
+
+
+def _oracle_fwd(q, k, v, scale, causal):
+    out, lse = orc.attention_forward(q, k, v, scale, causal)
+    # a row without a visible key: the kernels return LSE = 0 there; partial_attention never asks for such rows
+    return out.to(q.dtype), lse
+
+
+def _oracle_combine(o_accum, lse_accum, b, sq, h):
+    out, lse = orc.combine(o_accum, lse_accum)
+    d = out.shape[-1]
+    return out.view(b, h, sq, d).permute(0, 2, 1, 3).contiguous(), lse.view(b, h, sq)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, causal, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from flash_attention_turing_b200 import seq_parallel as sp
+
+        torch.manual_seed(5)  # same data on every rank
+        b, s, h, hk, d = 2, 64, 4, 2, 64
+        q = torch.randn(b, s, h, d)
+        k = torch.randn(b, s, hk, d)
+        v = torch.randn(b, s, hk, d)
+        shard = s // world
+        ks, vs = k[:, rank * shard:(rank + 1) * shard], v[:, rank * shard:(rank + 1) * shard]
+        out, lse = sp.sequence_parallel_forward(q, ks, vs, None, causal, gather_output=True,
+                                                fwd=_oracle_fwd, combine=_oracle_combine)
+        ref_out, ref_lse = orc.attention_forward(q, k, v, None, causal)
+        err_o = (out - ref_out).abs().max().item()
+        err_l = (lse - ref_lse).abs().max().item()
+        # slice-only result too
+        out_s, _ = sp.sequence_parallel_forward(q, ks, vs, None, causal, fwd=_oracle_fwd, combine=_oracle_combine)
+        sl = s // world
+        err_s = (out_s - ref_out[:, rank * sl:(rank + 1) * sl]).abs().max().item()
+        results[rank] = (err_o, err_l, err_s)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("causal", [False, True])
+def test_sequence_parallel_forward_matches_single_process(world, causal):
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), causal, results), nprocs=world, join=True)
+    assert len(results) == world
+    for rank in range(world):
+        err_o, err_l, err_s = results[rank]
+        assert err_o < 1e-5 and err_l < 1e-5 and err_s < 1e-5, (rank, err_o, err_l, err_s)
+
+
+def test_partial_attention_rows_before_the_shard_are_neutral():
+    from flash_attention_turing_b200 import seq_parallel as sp
+
+    torch.manual_seed(0)
+    q, k, v = torch.randn(1, 16, 2, 64), torch.randn(1, 4, 2, 64), torch.randn(1, 4, 2, 64)
+    out, lse = sp.partial_attention(q, k, v, key_offset=8, softmax_scale=0.125, causal=True, fwd=_oracle_fwd)
+    assert torch.isinf(lse[:, :, :8]).all() and (lse[:, :, :8] < 0).all()
+    assert out[:, :8].abs().max().item() == 0
+    assert torch.isfinite(lse[:, :, 8:]).all()

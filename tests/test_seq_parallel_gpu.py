@@ -1,0 +1,67 @@
+"""Sequence-sharded forward on two GPUs over NCCL, checked against the single-GPU kernel and the CPU
+oracle.  Skipped on a box with fewer than two GPUs."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, causal, d, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from flash_attention_turing_b200 import _ext, seq_parallel as sp
+        from oracle import attention_oracle as orc
+
+        ext = _ext.load()
+        gen = torch.Generator().manual_seed(11)  # same data on every rank
+        b, s, h, hk = 1, 1024, 4, 2
+        q = torch.randn(b, s, h, d, generator=gen).half()
+        k = torch.randn(b, s, hk, d, generator=gen).half()
+        v = torch.randn(b, s, hk, d, generator=gen).half()
+        shard = s // world
+        qd = q.to(dev)
+        ks = k[:, rank * shard:(rank + 1) * shard].contiguous().to(dev)
+        vs = v[:, rank * shard:(rank + 1) * shard].contiguous().to(dev)
+        out, lse = sp.sequence_parallel_forward(qd, ks, vs, None, causal, gather_output=True)
+        torch.cuda.synchronize()
+        ref_out, ref_lse = orc.attention_forward(q, k, v, None, causal)
+        one_out, _ = ext.fwd(qd, k.to(dev), v.to(dev), d ** -0.5, causal)
+        results[rank] = ((out.float().cpu() - ref_out).abs().max().item(),
+                         (lse.cpu() - ref_lse).abs().max().item(),
+                         (out.float() - one_out.float()).abs().max().item(),
+                         int(ext.device_status(True)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("d", [64, 128])
+def test_two_gpu_sequence_parallel_forward(causal, d):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), causal, d, results), nprocs=world, join=True)
+    for rank in range(world):
+        err_o, err_l, err_one, status = results[rank]
+        assert status == 0
+        assert err_o <= 3e-3, (rank, err_o)       # fp16 partials merged: two fp16 roundings
+        assert err_l <= 1e-3, (rank, err_l)
+        assert err_one <= 3e-3, (rank, err_one)
