@@ -36,6 +36,10 @@ constexpr int kNumThreads = 576;
 constexpr int kProducerWarp = 16;
 constexpr int kMmaWarp = 17;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+#ifndef FA_FWD_POLY_EVERY
+#define FA_FWD_POLY_EVERY 0
+#endif
+constexpr int kPolyEvery = FA_FWD_POLY_EVERY;  // 0: all exponentials on the ex2 unit; n: every n-th pair on the FMA pipe
 
 struct FwdKernelParams {
   CUtensorMap tm_q;
@@ -82,7 +86,7 @@ struct Cfg {
 struct Barriers {
   uint64_t q_full[kTiles];
   uint64_t s_full[kTiles];
-  uint64_t p_full[kTiles];
+  uint64_t p_full[kTiles][2];  // P chunk c (key slices {2c, 2c+1} of each 64-key half) written
   uint64_t o_full[kTiles];
   uint64_t x_full[kTiles];  // row-statistics exchange between the two column halves of a tile
   uint64_t k_full[4];
@@ -151,7 +155,8 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
     for (int t = 0; t < kTiles; ++t) {
       mbar_init(&bars->q_full[t], 1);
       mbar_init(&bars->s_full[t], 1);
-      mbar_init(&bars->p_full[t], 8);
+      mbar_init(&bars->p_full[t][0], 8);
+      mbar_init(&bars->p_full[t][1], 8);
       mbar_init(&bars->o_full[t], 1);
       mbar_init(&bars->x_full[t], 8);
     }
@@ -228,26 +233,32 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
       // S_t = Q_t K_j^T : D/16 MMAs of K=16; slice k lives in swizzle chunk k/4 at byte (k%4)*32.
       auto issue_qk = [&](int t, int j) {
         const int s = j % C::kStages;
-        const uint32_t qa = sQ_addr + t * C::kTileBytes;
-        const uint32_t ka = sK_addr + s * C::kTileBytes;
+        const uint64_t qd = make_smem_desc(sQ_addr + t * C::kTileBytes, 16, 1024);
+        const uint64_t kd = make_smem_desc(sK_addr + s * C::kTileBytes, 16, 1024);
+        const uint32_t d_addr = tmem_base + C::kColS + t * 128;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * C::kChunkBytes + (k & 3) * 32;
-          mma_ss(tmem_base + C::kColS + t * 128, make_smem_desc(qa + off, 16, 1024),
-                 make_smem_desc(ka + off, 16, 1024), idesc_qk, k > 0);
+          mma_ss(d_addr, desc_advance(qd, off), desc_advance(kd, off), idesc_qk, k > 0);
         }
       };
       // O_t += P_t V_j : 8 MMAs of K=16 keys; A slice k = 8 TMEM columns of packed fp16 (slices 0-3 at
       // the start of the first 64-column half of S_t, slices 4-7 at the start of the second half: each
       // half is written by the threads that own it); B slice k starts 16 key rows (2048 B) further,
       // head_dim chunks are kChunkBytes apart (LBO).
-      auto issue_pv = [&](int t, int j) {
+      // chunk c covers key slices {2c, 2c+1} (first 64-key half) and {4+2c, 4+2c+1} (second half): the
+      // softmax threads hand over P in two steps so that the first half of the PV MMAs runs under the
+      // exponentials of the second.
+      auto issue_pv = [&](int t, int j, int c) {
         const int s = j % C::kStages;
-        const uint32_t va = sV_addr + s * C::kTileBytes;
+        const uint64_t vd = make_smem_desc(sV_addr + s * C::kTileBytes, C::kChunkBytes, 1024);
+        const uint32_t d_addr = tmem_base + C::kColO + t * D;
+        const uint32_t a_addr = tmem_base + C::kColS + t * 128;
 #pragma unroll
-        for (int k = 0; k < kBlockN / 16; ++k) {
-          mma_ts(tmem_base + C::kColO + t * D, tmem_base + C::kColS + t * 128 + packed_slice_col(k),
-                 make_smem_desc(va + k * 2048, C::kChunkBytes, 1024), idesc_pv, (j > 0) || (k > 0));
+        for (int i = 0; i < 4; ++i) {
+          const int k = (i >> 1) * 4 + 2 * c + (i & 1);
+          mma_ts(d_addr, a_addr + packed_slice_col(k), desc_advance(vd, k * 2048), idesc_pv,
+                 (j > 0 || c > 0 || i > 0) ? 1u : 0u);
         }
       };
 
@@ -277,10 +288,13 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
 #pragma unroll
         for (int t = 0; t < kTiles; ++t) {
           if (j >= nb[t]) continue;
-          if (!(ok = mbar_wait(&bars->p_full[t], j & 1, ctx))) break;
+          if (!(ok = mbar_wait(&bars->p_full[t][0], j & 1, ctx))) break;
           if (!(ok = mbar_wait(&bars->v_full[s], ph, ctx))) break;
           tc_fence_after_sync();
-          issue_pv(t, j);
+          issue_pv(t, j, 0);
+          if (!(ok = mbar_wait(&bars->p_full[t][1], j & 1, ctx))) break;
+          tc_fence_after_sync();
+          issue_pv(t, j, 1);
           const bool last_user_v = (t == kTiles - 1) || !(j < nb[kTiles - 1]);
           if (last_user_v) tc_commit(&bars->v_empty[s]);
           if (j + 1 < nb[t]) {
@@ -401,7 +415,10 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const float2 x = ffma2(make_float2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), c2, nm2);
-          const float2 e = make_float2(ex2f(x.x), ex2f(x.y));
+          // every kPolyEvery-th pair goes to the FMA-pipe polynomial, the rest to the ex2 unit
+          const float2 e = (kPolyEvery > 0 && (i % (kPolyEvery > 0 ? kPolyEvery : 1)) == 0)
+                               ? exp2_poly2(x)
+                               : make_float2(ex2f(x.x), ex2f(x.y));
           lsum = fadd2(lsum, e);
           pk[i] = pack_half2(e.x, e.y);
         }
@@ -409,6 +426,10 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
         // chunk 1 on columns 16-31, both already consumed; the S columns 32-63 are read before they
         // could be touched.
         tmem_st16(tS + q * 16, pk);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_full[t][q]);
       };
       {
         uint32_t s1[32];
@@ -419,10 +440,6 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
         exp_store(s1, 1);
       }
       l += lsum.x + lsum.y;
-      tmem_wait_st();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->p_full[t]);
     }
 
     // ---- epilogue: total row sum from both halves, normalise, convert, store ----
