@@ -91,6 +91,9 @@ def test_cache_batch_idx_and_scale(ext):
 def test_uninitialised_cache_tail_is_never_used(ext):
     _run(2, 1, 4, 2, 128, 1024, [100, 777], 1, splits=1, poison_tail=True)
     _run(2, 1, 4, 2, 64, 1024, [100, 777], 1, splits=4, poison_tail=True)
+    # query chunks that go through the tiled tcgen05 kernel (more than 16 rows per KV head)
+    _run(2, 40, 4, 2, 128, 1024, [100, 777], 40, splits=0, poison_tail=True)
+    _run(2, 130, 4, 4, 64, 1024, [3, 500], 130, splits=0, poison_tail=True, causal=False)
 
 
 def test_int_and_default_cache_seqlens(ext):
