@@ -361,35 +361,6 @@ __device__ __forceinline__ float2 fsub2(float2 a, float2 b) {
       : "l"(reinterpret_cast<uint64_t&>(a)), "l"(reinterpret_cast<uint64_t&>(b)));
   return d;
 }
-__device__ __forceinline__ float2 fadd2_round_down(float2 a, float2 b) {
-  float2 d;
-  asm("add.rm.f32x2 %0, %1, %2;"
-      : "=l"(reinterpret_cast<uint64_t&>(d))
-      : "l"(reinterpret_cast<uint64_t&>(a)), "l"(reinterpret_cast<uint64_t&>(b)));
-  return d;
-}
-
-// 2^x for two values on the FMA / integer pipes instead of the (16 per clock per SM) ex2 unit.
-// x is clamped to >= -126, split into floor(x) + f with the add-magic-number trick (round toward
-// -inf at magnitude 1.5 * 2^23, where one ulp is 1), 2^f on [0, 1) is a cubic with maximum relative
-// error 8.6e-5 -- below the 4.9e-4 of the fp16 rounding P gets anyway -- and floor(x) is added into the
-// exponent field.  Valid for x <= 127; results for x < -126 are ~1e-38 instead of 0.
-__device__ __forceinline__ float2 exp2_poly2(float2 x) {
-  const float2 magic = make_float2(12582912.f, 12582912.f);  // 1.5 * 2^23
-  x.x = fmaxf(x.x, -126.f);
-  x.y = fmaxf(x.y, -126.f);
-  const float2 t = fadd2_round_down(x, magic);               // low mantissa bits = floor(x)
-  const float2 f = fsub2(x, fsub2(t, magic));                // fractional part in [0, 1)
-  float2 p = ffma2(make_float2(0.07706617563962936f, 0.07706617563962936f), f,
-                   make_float2(0.22764593362808228f, 0.22764593362808228f));
-  p = ffma2(p, f, make_float2(0.6951165795326233f, 0.6951165795326233f));
-  p = ffma2(p, f, make_float2(1.f, 1.f));
-  float2 r;
-  r.x = __uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23));
-  r.y = __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23));
-  return r;
-}
-
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
