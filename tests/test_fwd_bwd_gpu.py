@@ -255,3 +255,72 @@ def test_full_size_causal_config_by_sampling(ext, causal):
     ones = torch.ones_like(v)
     o1, _ = ext.fwd(q, k, ones, d ** -0.5, causal)
     assert (o1.float() - 1).abs().max().item() <= 2e-3
+
+
+def _c3_lengths():
+    """C3 of the benchmark configs: 16 sequences, lengths U[256, 4096] (seeded), capped at 32768 tokens."""
+    gen = torch.Generator().manual_seed(1003)
+    lens = torch.randint(256, 4097, (16,), generator=gen)
+    total = int(lens.sum())
+    if total > 32768:
+        lens = torch.clamp(lens * 32768 // total, min=256)
+    return [int(x) for x in lens]
+
+
+def test_c3_gqa_varlen_full_size(ext):
+    # C3: GQA varlen forward + backward, causal, Hq32 Hkv8 D128, 16 sequences.  The full-size launch is
+    # checked on two whole sequences (all heads of one KV group each) against the oracle.
+    from flash_attention_turing_b200 import flash_attn_varlen_func
+
+    lens = _c3_lengths()
+    assert sum(lens) <= 32768
+    h, hk, d = 32, 8, 128
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32)
+    total = int(cu[-1])
+    gen = torch.Generator(device=DEV).manual_seed(1003)
+    q = torch.randn(total, h, d, device=DEV, dtype=torch.half, generator=gen).requires_grad_(True)
+    k = torch.randn(total, hk, d, device=DEV, dtype=torch.half, generator=gen).requires_grad_(True)
+    v = torch.randn(total, hk, d, device=DEV, dtype=torch.half, generator=gen).requires_grad_(True)
+    dout = torch.randn(total, h, d, device=DEV, dtype=torch.half, generator=gen)
+    out = flash_attn_varlen_func(q, k, v, cu.to(DEV), cu.to(DEV), max(lens), max(lens), causal=True)
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), dout)
+    order = sorted(range(16), key=lambda i: lens[i])
+    for seq, kv_head in ((order[0], 0), (order[8], 5)):
+        a, b = int(cu[seq]), int(cu[seq + 1])
+        hs = slice(kv_head * 4, kv_head * 4 + 4)
+        qs, ks, vs, ds = (x.detach()[a:b].cpu() for x in (q[:, hs], k[:, kv_head:kv_head + 1], v[:, kv_head:kv_head + 1], dout[:, hs]))
+        o_ref, _ = orc.attention_forward_one(qs, ks, vs, d ** -0.5, True)
+        rq, rk, rv = orc.attention_backward_one(qs, ks, vs, ds, d ** -0.5, True)
+        _check("O", out[a:b, hs], o_ref)
+        _check("dQ", dq[a:b, hs], rq)
+        _check("dK", dk[a:b, kv_head:kv_head + 1], rk, max_tol=2 * MAX_ABS_TOL)
+        _check("dV", dv[a:b, kv_head:kv_head + 1], rv, max_tol=2 * MAX_ABS_TOL)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_c5_long_context_by_sampling(ext, d):
+    # C5: B1 S65536 H16 causal, forward + backward at full size on a head shard (2 of 16 heads, as one rank
+    # of an 8-GPU head-sharded run).  The oracle is evaluated on sampled query rows (forward) and through
+    # size-independent properties (backward): with V = 1 the output is 1, and the gradients of the
+    # linear functional sum(O * dO) must satisfy sum(dQ * Q) = sum(dK * K) (scores depend on Q K^T only).
+    b, s, h = 1, 65536, 2
+    gen = torch.Generator(device=DEV).manual_seed(1005)
+    q, k, v, dout = (torch.randn(b, s, h, d, device=DEV, dtype=torch.half, generator=gen) for _ in range(4))
+    out, lse = ext.fwd(q, k, v, d ** -0.5, True)
+    rows = [0, 1, 127, 128, 4095, 30000, 65535]
+    for r in rows:
+        qs = q[:, r:r + 1, :1].cpu()
+        o_ref, lse_ref = orc.attention_forward(qs, k[:, : r + 1, :1].cpu(), v[:, : r + 1, :1].cpu(), None, False)
+        assert err_stats(out[:, r:r + 1, :1], o_ref)[0] <= MAX_ABS_TOL
+        assert err_stats(lse[:, :1, r:r + 1], lse_ref)[0] <= LSE_TOL
+    o1, _ = ext.fwd(q, k, torch.ones_like(v), d ** -0.5, True)
+    assert (o1.float() - 1).abs().max().item() <= 2e-3
+    dq, dk, dv = ext.bwd(q, k, v, out, lse, dout, d ** -0.5, True)
+    assert not any(torch.isnan(x).any().item() for x in (dq, dk, dv))
+    lhs = (dq.float() * q.float()).sum().item()
+    rhs = (dk.float() * k.float()).sum().item()
+    assert abs(lhs - rhs) <= 2e-3 * max(abs(lhs), abs(rhs), (dq.float().abs() * q.float().abs()).sum().item() * 1e-3)
+    # dV of the last key row is exactly P[last query, last key] * dO[last query] = softmax weight of one element
+    p_last = torch.exp((q[0, -1].float() * k[0, -1].float()).sum(-1) * d ** -0.5 - lse[0, :, -1])
+    want = p_last[:, None] * dout[0, -1].float()
+    assert (dv[0, -1].float() - want).abs().max().item() <= 1e-3

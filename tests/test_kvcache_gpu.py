@@ -156,3 +156,39 @@ def test_cache_batch_idx_out_of_range_is_rejected_on_the_host(ext):
     with pytest.raises(RuntimeError, match="within cache batch bounds"):
         flash_attn_with_kvcache(q, kc, kc.clone(), cache_seqlens=torch.tensor([4], dtype=torch.int32, device=DEV),
                                 cache_batch_idx=torch.tensor([2], dtype=torch.int32, device=DEV))
+
+
+@pytest.mark.parametrize("splits", [1, 4, 16])
+def test_c4_paged_decode_full_size(ext, splits):
+    # C4 of the benchmark configs: batch 64, one query token, Hq32 Hkv8 D128, cache_seqlens U[1024, 32768],
+    # page 256, 16384-page pool, shuffled block table, in-place append.  Four sequences are checked against
+    # the oracle (gathering their pages on the CPU); the appended rows of the pool must hold k/v exactly.
+    from flash_attention_turing_b200 import flash_attn_with_kvcache
+
+    b, h, hk, d, page, pages, max_pages = 64, 32, 8, 128, 256, 16384, 129
+    gen_c = torch.Generator().manual_seed(1004)
+    lens = torch.randint(1024, 32768, (b,), generator=gen_c, dtype=torch.int32)
+    perm = torch.randperm(pages, generator=gen_c).to(torch.int32)
+    table = torch.zeros(b, max_pages, dtype=torch.int32)
+    off = 0
+    for i in range(b):
+        n = (int(lens[i]) + 1 + page - 1) // page
+        table[i, :n] = perm[off:off + n]
+        off += n
+    gen = torch.Generator(device=DEV).manual_seed(1004)
+    kc = torch.randn(pages, page, hk, d, device=DEV, dtype=torch.half, generator=gen)
+    vc = torch.randn(pages, page, hk, d, device=DEV, dtype=torch.half, generator=gen)
+    q = torch.randn(b, 1, h, d, device=DEV, dtype=torch.half, generator=gen)
+    kn = torch.randn(b, 1, hk, d, device=DEV, dtype=torch.half, generator=gen)
+    vn = torch.randn(b, 1, hk, d, device=DEV, dtype=torch.half, generator=gen)
+    out, lse = flash_attn_with_kvcache(q, kc, vc, kn, vn, cache_seqlens=lens.to(DEV), block_table=table.to(DEV),
+                                       causal=True, num_splits=splits, return_softmax_lse=True)
+    for i in (0, 17, 40, 63):
+        n_tok = int(lens[i]) + 1
+        ids = table[i, : (n_tok + page - 1) // page].to(DEV).long()
+        ks = kc[ids].reshape(-1, hk, d)[:n_tok].cpu()
+        vs = vc[ids].reshape(-1, hk, d)[:n_tok].cpu()
+        assert torch.equal(ks[-1], kn[i, 0].cpu()) and torch.equal(vs[-1], vn[i, 0].cpu())  # appended in place
+        o_ref, lse_ref = orc.attention_forward_one(q[i].cpu(), ks, vs, d ** -0.5, True)
+        assert err_stats(out[i], o_ref)[0] <= O_TOL
+        assert err_stats(lse[i], lse_ref)[0] <= LSE_TOL
