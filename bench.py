@@ -211,6 +211,98 @@ def run_profile_case(args):
     print(json.dumps({"profile": args.profile, "device_status": lib.fa_device_status(1)}))
 
 
+def run_all_configs(args):
+    """CUDA-event timings of the five configs of BASELINE.json on cuda:0 (forward, backward, decode).
+    One JSON line per config; burst numbers (20 iterations each), not the sustained headline loop."""
+    import torch
+
+    from flash_attention_turing_b200 import _ext, flash_attn_with_kvcache
+
+    ext = _ext.load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev).manual_seed(1)
+
+    def time_ms(fn, iters=20, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    def dense(name, b, s, h, hk, d, causal, with_bwd, iters=20):
+        q = torch.randn(b, s, h, d, device=dev, dtype=torch.half, generator=gen)
+        k = torch.randn(b, s, hk, d, device=dev, dtype=torch.half, generator=gen)
+        v = torch.randn(b, s, hk, d, device=dev, dtype=torch.half, generator=gen)
+        do = torch.randn_like(q)
+        scale = d ** -0.5
+        out, lse = ext.fwd(q, k, v, scale, causal)
+        f = fwd_flops(b, h, s, s, d, causal)
+        rec = {"config": name, "fwd_ms": time_ms(lambda: ext.fwd(q, k, v, scale, causal), iters)}
+        rec["fwd_tflops"] = f / rec["fwd_ms"] / 1e9
+        if with_bwd:
+            rec["bwd_ms"] = time_ms(lambda: ext.bwd(q, k, v, out, lse, do, scale, causal), iters)
+            rec["bwd_tflops"] = 2.5 * f / rec["bwd_ms"] / 1e9
+        print(json.dumps(rec), flush=True)
+
+    dense("C1 fwd non-causal B2 S512 H8 D64", 2, 512, 8, 8, 64, False, False)
+    dense("C2 fwd+bwd causal B4 S4096 H32 D128", 4, 4096, 32, 32, 128, True, True)
+    dense("H8K fwd+bwd causal B4 S8192 H32 D128", 4, 8192, 32, 32, 128, True, True)
+    # C3: GQA varlen
+    g3 = torch.Generator().manual_seed(1003)
+    lens = torch.randint(256, 4097, (16,), generator=g3)
+    if int(lens.sum()) > 32768:
+        lens = torch.clamp(lens * 32768 // int(lens.sum()), min=256)
+    cu = torch.tensor([0] + lens.cumsum(0).tolist(), dtype=torch.int32, device=dev)
+    total, mx = int(lens.sum()), int(lens.max())
+    q = torch.randn(total, 32, 128, device=dev, dtype=torch.half, generator=gen)
+    k = torch.randn(total, 8, 128, device=dev, dtype=torch.half, generator=gen)
+    v = torch.randn(total, 8, 128, device=dev, dtype=torch.half, generator=gen)
+    do = torch.randn_like(q)
+    sc = 128 ** -0.5
+    out, lse = ext.varlen_fwd(q, k, v, cu, cu, mx, mx, sc, True)
+    f3 = float(sum(4.0 * 32 * int(n) ** 2 * 128 * 0.5 for n in lens))
+    rec = {"config": f"C3 GQA varlen causal Hq32 Hkv8 D128, 16 seqs, {total} tokens",
+           "fwd_ms": time_ms(lambda: ext.varlen_fwd(q, k, v, cu, cu, mx, mx, sc, True)),
+           "bwd_ms": time_ms(lambda: ext.varlen_bwd(q, k, v, out, lse, do, cu, cu, mx, mx, sc, True))}
+    rec["fwd_tflops"] = f3 / rec["fwd_ms"] / 1e9
+    rec["bwd_tflops"] = 2.5 * f3 / rec["bwd_ms"] / 1e9
+    print(json.dumps(rec), flush=True)
+    del q, k, v, do, out, lse
+    # C5: long context, head shard of an 8-GPU run (2 of 16 heads) and the full 16 heads on one GPU
+    for d in (128, 64):
+        dense(f"C5 fwd+bwd causal B1 S65536 H16 D{d} (all 16 heads on one GPU)", 1, 65536, 16, 16, d, True, True, iters=3)
+    # C4: paged decode through the public API (includes its host-side checks)
+    c = DECODE
+    gen_c = torch.Generator().manual_seed(1004)
+    lens4 = torch.randint(c["lo"], c["hi"], (c["b"],), generator=gen_c, dtype=torch.int32)
+    perm = torch.randperm(c["pages"], generator=gen_c).to(torch.int32)
+    table = torch.zeros(c["b"], c["max_pages"], dtype=torch.int32)
+    off = 0
+    for i in range(c["b"]):
+        n = (int(lens4[i]) + 1 + c["page"] - 1) // c["page"]
+        table[i, :n] = perm[off:off + n]
+        off += n
+    kc = torch.randn(c["pages"], c["page"], c["h_k"], c["d"], device=dev, dtype=torch.half, generator=gen)
+    vc = torch.randn(c["pages"], c["page"], c["h_k"], c["d"], device=dev, dtype=torch.half, generator=gen)
+    q1 = torch.randn(c["b"], 1, c["h"], c["d"], device=dev, dtype=torch.half, generator=gen)
+    kn = torch.randn(c["b"], 1, c["h_k"], c["d"], device=dev, dtype=torch.half, generator=gen)
+    vn = torch.randn_like(kn)
+    ld, td = lens4.to(dev), table.to(dev)
+    kv_bytes = float((lens4.double() + 1).sum()) * 2 * c["h_k"] * c["d"] * 2
+    for splits in (1, 4, 16, 0):
+        ms = time_ms(lambda: flash_attn_with_kvcache(q1, kc, vc, kn, vn, cache_seqlens=ld, block_table=td, causal=True,
+                                                     num_splits=splits))
+        print(json.dumps({"config": f"C4 paged decode B64 Hq32 Hkv8 D128 num_splits={splits} (public API)",
+                          "ms": ms, "kv_gbs": kv_bytes / ms / 1e6}), flush=True)
+    print(json.dumps({"device_status": int(ext.device_status(True))}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -222,9 +314,14 @@ def main():
     ap.add_argument("--profile", choices=["fwd", "bwd", "decode"], default=None,
                     help="run a few launches of one kernel group on a reduced case and exit (for ncu captures)")
     ap.add_argument("--profile-iters", type=int, default=3)
+    ap.add_argument("--configs", action="store_true",
+                    help="time the five benchmark configs (C1..C5) through the torch binding on one GPU and exit")
     args = ap.parse_args()
     if args.profile:
         run_profile_case(args)
+        return
+    if args.configs:
+        run_all_configs(args)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
