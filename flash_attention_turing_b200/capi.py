@@ -41,7 +41,7 @@ class FaFwdParams(C.Structure):
            ("h_k", _i32), ("d", _i32), ("total_q", _i32), ("total_k", _i32), ("k_batch", _i32),
            ("softmax_scale", _f32), ("is_causal", _i32), ("cu_seqlens_q", _vp), ("cu_seqlens_k", _vp),
            ("seqused_k", _vp), ("cache_batch_idx", _vp), ("block_table", _vp),
-           ("block_table_batch_stride", _i64), ("page_size", _i32), ("reserved0", _i32)]
+           ("block_table_batch_stride", _i64), ("page_size", _i32), ("block_table_cols", _i32)]
     )
 
 

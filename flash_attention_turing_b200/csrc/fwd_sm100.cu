@@ -54,6 +54,7 @@ struct FwdKernelParams {
   const int* cu_seqlens_k;
   const int* seqused_k;
   int seqused_k_add;  // added to seqused_k[b] (tokens appended to a cache in the same call)
+  int k_capacity;     // upper bound for seqused_k: rows of k, or block_table columns * page_size
   const int* cache_batch_idx;
   const int* block_table;
   int64_t block_table_batch_stride;
@@ -106,10 +107,15 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
   const int sq = varlen_q ? p.cu_seqlens_q[batch + 1] - q_off : p.seqlen_q;
   const int k_off = varlen_k ? p.cu_seqlens_k[batch] : 0;
   int sk = varlen_k ? p.cu_seqlens_k[batch + 1] - k_off : p.seqlen_k;
-  if (p.seqused_k) sk = p.seqused_k[batch] + p.seqused_k_add;
+  if (p.seqused_k) {
+    // clamped to what the K/V tensor (or the block table) can hold; a clamp is reported in the status word
+    const int raw = p.seqused_k[batch] + p.seqused_k_add;
+    sk = max(0, min(raw, p.k_capacity));
+    if (sk != raw && threadIdx.x == 0 && p.status) atomicOr(p.status, kStatusCapacityClamped);
+  }
   const int row0 = mpair * (kTiles * kBlockM);
   if (row0 >= sq) return;
-  if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;
+  if (p.status && (*reinterpret_cast<volatile int*>(p.status) & kStatusWaitTimeout) != 0) return;
 
   const int bq = varlen_q ? 0 : batch;
   const int bk = varlen_k ? 0 : (p.cache_batch_idx ? p.cache_batch_idx[batch] : batch);
@@ -649,6 +655,8 @@ int run_fwd(const FaFwdParams* p, int seqused_k_add, cudaStream_t stream) {
   kp.cu_seqlens_k = p->cu_seqlens_k;
   kp.seqused_k = p->seqused_k;
   kp.seqused_k_add = seqused_k_add;
+  kp.k_capacity = (p->block_table && p->block_table_cols > 0) ? p->block_table_cols * p->page_size
+                  : (p->block_table ? 0x7fffffff : static_cast<int>(k_rows));
   kp.cache_batch_idx = p->cache_batch_idx;
   kp.block_table = p->block_table;
   kp.block_table_batch_stride = p->block_table_batch_stride;

@@ -54,6 +54,7 @@ struct DecodeParams {
   const int* block_table;
   int64_t block_table_batch_stride;
   int page_size;     // tokens per page (paged) or capacity per cache row (contiguous)
+  int capacity;      // tokens a sequence can hold: max_blocks_per_seq * page_size, or the cache row length
   int num_splits;    // grid.x
   int chunk_tiles;   // > 0: split s owns tiles [s*chunk, (s+1)*chunk); 0: proportional ranges
   int* status;
@@ -117,7 +118,11 @@ decode_kernel(const __grid_constant__ DecodeParams p) {
   const int rows = p.seqlen_q * p.group;  // valid rows of the 16-row M tile
 
   // ---- this CTA's token range ----
-  const int len = p.cache_seqlens[batch] + p.seqlen_new;
+  // Lengths are clamped to the cache capacity on the device (the host does not have to read them back);
+  // a clamp is reported through the status word.
+  const int len_raw = p.cache_seqlens[batch] + p.seqlen_new;
+  const int len = max(0, min(len_raw, p.capacity));
+  if (len != len_raw && threadIdx.x == 0 && p.status) atomicOr(p.status, kStatusCapacityClamped);
   const int n_tiles = (len + kTileTokens - 1) / kTileTokens;
   int tile_begin, tile_end;
   if (p.chunk_tiles > 0) {
@@ -136,7 +141,7 @@ decode_kernel(const __grid_constant__ DecodeParams p) {
     return (static_cast<int64_t>(batch) * p.h + head) * p.seqlen_q + q_pos;
   };
 
-  if (my_tiles <= 0 || (p.status && *reinterpret_cast<volatile int*>(p.status) != 0)) {
+  if (my_tiles <= 0 || (p.status && (*reinterpret_cast<volatile int*>(p.status) & kStatusWaitTimeout) != 0)) {
     // empty split: neutral partial (or a zero row when there is nothing to attend to at all)
     for (int idx = threadIdx.x; idx < rows * (D / 2); idx += blockDim.x) {
       const int r = idx / (D / 2);
@@ -656,6 +661,7 @@ extern "C" int fa_kvcache(const FaKvcacheParams* p, fa_stream_t stream_) {
     f.block_table = p->block_table;
     f.block_table_batch_stride = p->block_table_batch_stride;
     f.page_size = p->block_table ? p->seqlen_cache : 0;
+    f.block_table_cols = p->block_table ? p->max_blocks_per_seq : 0;
     return run_fwd(&f, p->seqlen_new, stream);
   }
 
@@ -698,6 +704,7 @@ extern "C" int fa_kvcache(const FaKvcacheParams* p, fa_stream_t stream_) {
   dp.block_table = p->block_table;
   dp.block_table_batch_stride = p->block_table_batch_stride;
   dp.page_size = p->seqlen_cache;
+  dp.capacity = capacity_tokens(p);
   dp.num_splits = splits;
   dp.chunk_tiles = chunk;
   dp.status = device_status_ptr();

@@ -16,7 +16,8 @@ namespace fa {
 // ---------------------------------------------------------------------------------------------
 enum : int {
   kStatusOk = 0,
-  kStatusWaitTimeout = 1,
+  kStatusWaitTimeout = 1,     // bit 0: a bounded wait gave up; later CTAs return at once, outputs are invalid
+  kStatusCapacityClamped = 2, // bit 1: a cache length exceeded the cache capacity and was clamped on the device
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -102,7 +103,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
         t0 = now;
       } else if (now - t0 > 4000000000ull) {
         *ctx.abort_flag = 1;
-        if (ctx.status) atomicCAS(ctx.status, kStatusOk, kStatusWaitTimeout);
+        if (ctx.status) atomicOr(ctx.status, kStatusWaitTimeout);
         return false;
       }
     }

@@ -22,6 +22,14 @@ import torch
 from . import _ext
 
 
+# The reference reads cache_seqlens back to the host to check the cache capacity on every call
+# (``int(cache_seqlens.max().item())``, its :855) -- a device synchronisation per decode step.  The check
+# is part of the reference's error contract, so it stays on by default.  A serving loop that guarantees
+# capacity itself can set this to False: the kernels then clamp every length to the capacity on the device
+# (never reading or writing out of bounds) and report a clamp through ``device_status()`` bit 1.
+HOST_CAPACITY_CHECK = True
+
+
 def _gpu():
     """The torch binding (loaded on first use so that argument validation works without a GPU)."""
     return _ext.load()
@@ -361,9 +369,10 @@ def flash_attn_with_kvcache(
         seqlen_new = k.shape[1]
     # Capacity is checked before the device/dtype checks, on whatever device the lengths live
     # (the reference does the same, :855-858, and its tests rely on that order with CPU tensors).
-    used = int(cache_seqlens.max().item()) if cache_seqlens.numel() > 0 else 0
-    if used + seqlen_new > capacity:
-        raise ValueError("cache capacity is insufficient for the requested append length")
+    if HOST_CAPACITY_CHECK or not cache_seqlens.is_cuda:
+        used = int(cache_seqlens.max().item()) if cache_seqlens.numel() > 0 else 0
+        if used + seqlen_new > capacity:
+            raise ValueError("cache capacity is insufficient for the requested append length")
 
     if not (q.is_cuda and k_cache.is_cuda and v_cache.is_cuda):
         raise RuntimeError("q, k_cache, v_cache must be CUDA tensors")

@@ -45,8 +45,11 @@ int fa_abi_version(void);
 
 /* Kernels never trap: every device-side wait (mbarrier, pipeline stage) is bounded, and a wait that
  * gives up records a non-zero code in a per-device status word and lets the kernel return.  This
- * call synchronises the current device and returns that word (0 = no kernel reported a problem,
- * 1 = a wait timed out and the outputs of that launch are invalid, negative = FA_ERR_*).  With
+ * call synchronises the current device and returns that word: 0 = no kernel reported a problem; bit 0
+ * (value 1) = a wait timed out and the outputs of that launch are invalid; bit 1 (value 2) = a cache
+ * length (cache_seqlens + seqlen_new, or seqused_k) exceeded the cache capacity and was clamped on the
+ * device, so that a host that skips the reference's synchronising capacity check
+ * (csrc/flash_attn/flash_api.cpp:627) still never reads or writes out of bounds; negative = FA_ERR_*.  With
  * reset != 0 the word is cleared afterwards.  No counterpart in the reference, whose launches are
  * not error-checked at all (src/flash_fwd_launch_template.h:73-89). */
 int fa_device_status(int reset);
@@ -84,7 +87,7 @@ typedef struct FaFwdParams {
   const int32_t* block_table;  /* (b, block_table_batch_stride) page ids, or NULL               */
   int64_t block_table_batch_stride;
   int32_t page_size;           /* tokens per page (multiple of 128) when block_table != NULL    */
-  int32_t reserved0;
+  int32_t block_table_cols;    /* columns of block_table (0 = unknown: seqused_k is trusted)    */
 } FaFwdParams;
 
 int fa_fwd(const FaFwdParams* p, fa_stream_t stream);

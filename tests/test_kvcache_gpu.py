@@ -192,3 +192,31 @@ def test_c4_paged_decode_full_size(ext, splits):
         o_ref, lse_ref = orc.attention_forward_one(q[i].cpu(), ks, vs, d ** -0.5, True)
         assert err_stats(out[i], o_ref)[0] <= O_TOL
         assert err_stats(lse[i], lse_ref)[0] <= LSE_TOL
+
+
+def test_device_side_capacity_clamp_without_host_check(ext):
+    # With the host-side capacity check switched off (no device synchronisation per call) an oversized
+    # length must neither read nor write out of bounds: it is clamped to the capacity on the device, the
+    # result equals the one for the clamped length, and bit 1 of the status word reports the clamp.
+    from flash_attention_turing_b200 import flash_attention_interface as iface
+
+    gen = torch.Generator().manual_seed(4)
+    b, h, hk, d, page, per = 2, 4, 2, 128, 256, 2
+    kc, vc = randn_half(gen, b * per, page, hk, d), randn_half(gen, b * per, page, hk, d)
+    table = torch.arange(b * per, dtype=torch.int32).view(b, per)
+    q = randn_half(gen, b, 1, h, d)
+    lens_bad = torch.tensor([300, 9999], dtype=torch.int32)       # capacity is 512 tokens per sequence
+    lens_ok = torch.tensor([300, 512], dtype=torch.int32)
+    o_ref, _ = orc.kvcache_forward(q, kc.clone(), vc.clone(), None, None, lens_ok, None, table, None, True)
+    iface.HOST_CAPACITY_CHECK = False
+    try:
+        out = iface.flash_attn_with_kvcache(q.to(DEV), kc.to(DEV), vc.to(DEV), cache_seqlens=lens_bad.to(DEV),
+                                            block_table=table.to(DEV), causal=True, num_splits=2)
+        status = ext.device_status(True)
+    finally:
+        iface.HOST_CAPACITY_CHECK = True
+    assert status == 2
+    assert err_stats(out, o_ref)[0] <= O_TOL
+    with pytest.raises(ValueError, match="cache capacity is insufficient"):
+        iface.flash_attn_with_kvcache(q.to(DEV), kc.to(DEV), vc.to(DEV), cache_seqlens=lens_bad.to(DEV),
+                                      block_table=table.to(DEV), causal=True)
