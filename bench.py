@@ -303,6 +303,94 @@ def run_all_configs(args):
     print(json.dumps({"device_status": int(ext.device_status(True))}))
 
 
+def run_sharded(args):
+    """The long-context config C5 (B1 S65536 H16 D128 causal) on N GPUs, one rank per GPU (torchrun):
+    (1) head-sharded forward + backward, 16/N heads per rank, no communication (strong scaling);
+    (2) sequence-sharded forward: K/V split into N contiguous ranges, every rank attends all queries against
+        its range, then the partial (O, LSE) are merged -- once with all_to_all_single + fa_combine (NCCL) and
+        once with the fused kernel that reads the peers' partials in place (fa_combine_gather).
+    Times are CUDA events, max over ranks; rank 0 prints one JSON line per measurement."""
+    import torch
+    import torch.distributed as dist
+
+    from flash_attention_turing_b200 import _ext, seq_parallel as sp
+
+    ext = _ext.load()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=dev)
+    s, h, d = 65536, 16, 128
+    scale = d ** -0.5
+
+    def timed(fn, iters=3, warm=1):
+        for _ in range(warm):
+            fn()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        if world > 1:
+            x = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(x, op=dist.ReduceOp.MAX)
+            ms = float(x.item())
+        return ms
+
+    gen = torch.Generator(device=dev).manual_seed(1005)
+    f_fwd = fwd_flops(1, h, s, s, d, True)
+    # (1) heads sharded
+    hl = max(1, h // world)
+    q, k, v, do = (torch.randn(1, s, hl, d, device=dev, dtype=torch.half, generator=gen) for _ in range(4))
+    out, lse = ext.fwd(q, k, v, scale, True)
+    fwd_ms = timed(lambda: ext.fwd(q, k, v, scale, True))
+    bwd_ms = timed(lambda: ext.bwd(q, k, v, out, lse, do, scale, True))
+    if rank == 0:
+        print(json.dumps({"workload": "C5 head-sharded fwd+bwd (B1 S65536 H16 D128 causal)", "n_gpus": world,
+                          "heads_per_gpu": hl, "scaling": "strong", "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+                          "fwd_tflops": f_fwd * (hl * world / h) / fwd_ms / 1e9,
+                          "bwd_tflops": 2.5 * f_fwd * (hl * world / h) / bwd_ms / 1e9}), flush=True)
+    del q, k, v, do, out, lse
+    # (2) sequence sharded forward (same q on every rank, K/V shard per rank)
+    if world > 1:
+        gq = torch.Generator(device=dev).manual_seed(77)
+        q = torch.randn(1, s, h, d, device=dev, dtype=torch.half, generator=gq)
+        shard = s // world
+        ks = torch.randn(1, shard, h, d, device=dev, dtype=torch.half, generator=gen)
+        vs = torch.randn(1, shard, h, d, device=dev, dtype=torch.half, generator=gen)
+        ms_a2a = timed(lambda: sp.sequence_parallel_forward(q, ks, vs, scale, True))
+        rec = {"workload": "C5 sequence-sharded forward (contiguous K/V ranges; causal work is unbalanced by design)",
+               "n_gpus": world, "merge_all_to_all_ms": ms_a2a, "fwd_tflops_all_to_all": f_fwd / ms_a2a / 1e9}
+        try:
+            o_ref, l_ref = sp.sequence_parallel_forward(q, ks, vs, scale, True)
+            o_p2p, l_p2p = sp.sequence_parallel_forward_p2p(q, ks, vs, scale, True)
+            rec["p2p_vs_all_to_all_max_abs_diff"] = float((o_p2p.float() - o_ref.float()).abs().max().item())
+            ms_p2p = timed(lambda: sp.sequence_parallel_forward_p2p(q, ks, vs, scale, True))
+            rec.update({"merge_peer_read_ms": ms_p2p, "fwd_tflops_peer_read": f_fwd / ms_p2p / 1e9})
+            # the merge step alone
+            part_ms = timed(lambda: sp.partial_attention(q, ks, vs, rank * shard, scale, True))
+            rec["partial_attention_ms"] = part_ms
+        except Exception as exc:  # noqa: BLE001  symmetric memory not usable here
+            rec["peer_read_unavailable"] = repr(exc)[:300]
+        if rank == 0:
+            print(json.dumps(rec), flush=True)
+    if rank == 0:
+        print(json.dumps({"device_status": int(ext.device_status(True))}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -314,6 +402,9 @@ def main():
     ap.add_argument("--profile", choices=["fwd", "bwd", "decode"], default=None,
                     help="run a few launches of one kernel group on a reduced case and exit (for ncu captures)")
     ap.add_argument("--profile-iters", type=int, default=3)
+    ap.add_argument("--sharded", action="store_true",
+                    help="multi-GPU runs of the long-context config (B1 S65536 H16 D128 causal): head-sharded forward + "
+                         "backward (no communication) and the sequence-sharded forward with its (O, LSE) merge")
     ap.add_argument("--configs", action="store_true",
                     help="time the five benchmark configs (C1..C5) through the torch binding on one GPU and exit")
     args = ap.parse_args()
@@ -322,6 +413,9 @@ def main():
         return
     if args.configs:
         run_all_configs(args)
+        return
+    if args.sharded:
+        run_sharded(args)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 

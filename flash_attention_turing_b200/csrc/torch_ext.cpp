@@ -408,6 +408,40 @@ std::vector<at::Tensor> combine(at::Tensor o_accum, at::Tensor lse_accum, int64_
   return {out, lse};
 }
 
+// ---- merge of per-rank partials read in place (o_parts[r] may be peer-mapped memory of another GPU) ----
+std::vector<at::Tensor> combine_gather(std::vector<at::Tensor> o_parts, std::vector<at::Tensor> lse_parts,
+                                       int64_t row_begin, int64_t rows) {
+  TORCH_CHECK(!o_parts.empty() && o_parts.size() == lse_parts.size(), "o_parts and lse_parts must have the same non-zero length");
+  TORCH_CHECK(o_parts.size() <= FA_MAX_GATHER_PARTS, "at most ", FA_MAX_GATHER_PARTS, " parts");
+  const at::Tensor& o0 = o_parts[0];
+  TORCH_CHECK(o0.dim() == 4, "partial O must be (b, seqlen_q, h, d)");
+  const int64_t b = o0.size(0), s = o0.size(1), h = o0.size(2), d = o0.size(3);
+  check_supported_head_dim(d);
+  FaCombineGatherParams p = {};
+  for (size_t i = 0; i < o_parts.size(); ++i) {
+    TORCH_CHECK(o_parts[i].is_cuda() && o_parts[i].scalar_type() == at::kHalf && o_parts[i].is_contiguous() &&
+                    o_parts[i].sizes() == o0.sizes(),
+                "partial O tensors must be contiguous float16 CUDA tensors of one shape");
+    TORCH_CHECK(lse_parts[i].is_cuda() && lse_parts[i].scalar_type() == at::kFloat && lse_parts[i].is_contiguous() &&
+                    lse_parts[i].dim() == 3 && lse_parts[i].size(0) == b && lse_parts[i].size(1) == h && lse_parts[i].size(2) == s,
+                "partial LSE tensors must be contiguous float32 (b, h, seqlen_q) CUDA tensors");
+    p.o_part[i] = o_parts[i].data_ptr();
+    p.lse_part[i] = lse_parts[i].data_ptr<float>();
+  }
+  TORCH_CHECK(row_begin >= 0 && rows >= 0 && row_begin + rows <= s, "row range out of bounds");
+  // outputs live on the CURRENT device (the partial tensors may be views of peer memory)
+  auto opts = at::TensorOptions().device(at::kCUDA, at::cuda::current_device());
+  at::Tensor out = torch::empty({b, rows, h, d}, opts.dtype(torch::kFloat16));
+  at::Tensor lse = torch::empty({b, h, rows}, opts.dtype(torch::kFloat32));
+  p.o = out.data_ptr();
+  p.lse = lse.data_ptr<float>();
+  p.num_parts = static_cast<int32_t>(o_parts.size());
+  p.b = b; p.h = h; p.seqlen_q = s; p.d = d;
+  p.row_begin = row_begin; p.rows = rows;
+  check_rc(fa_combine_gather(&p, current_stream()), "fa_combine_gather");
+  return {out, lse};
+}
+
 int64_t device_status(bool reset) { return fa_device_status(reset ? 1 : 0); }
 
 }  // namespace
@@ -419,5 +453,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("varlen_bwd", &mha_varlen_bwd, "Varlen backward pass");
   m.def("fwd_kvcache", &mha_fwd_kvcache, "KV-cache forward pass");
   m.def("combine", &combine, "Merge split partials (O fp32, LSE) with log-sum-exp weights");
+  m.def("combine_gather", &combine_gather, "Merge per-rank partial (O fp16, LSE) read in place, peer memory allowed");
   m.def("device_status", &device_status, "Synchronise and read the device status word");
 }

@@ -40,7 +40,8 @@ def _default_combine(o_accum, lse_accum, b, sq, h):
 
 
 def partial_attention(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, key_offset: int,
-                      softmax_scale: float, causal: bool, fwd: Optional[FwdFn] = None
+                      softmax_scale: float, causal: bool, fwd: Optional[FwdFn] = None,
+                      out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None
                       ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Attention of all queries against one K/V shard that starts at global key index ``key_offset``.
 
@@ -53,13 +54,20 @@ def partial_attention(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Ten
     fwd = fwd or _default_fwd
     b, s, h, d = q.shape
     s_shard = k_shard.shape[1]
-    out = torch.zeros_like(q)
-    lse = torch.full((b, h, s), float("-inf"), dtype=torch.float32, device=q.device)
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None:
+        lse = torch.empty((b, h, s), dtype=torch.float32, device=q.device)
+    if s_shard == 0 or causal:
+        out.zero_()
+        lse.fill_(float("-inf"))
     if s_shard == 0:
         return out, lse
     if not causal:
         o, l = fwd(q, k_shard, v_shard, softmax_scale, False)
-        return o, l
+        out.copy_(o)
+        lse.copy_(l)
+        return out, lse
     lo = min(key_offset, s)
     mid = min(key_offset + s_shard, s)
     if mid > lo:  # diagonal block: square causal problem
@@ -116,3 +124,52 @@ def sequence_parallel_forward(q: torch.Tensor, k_shard: torch.Tensor, v_shard: t
     dist.all_gather(outs, out, group=group)
     dist.all_gather(lses, lse, group=group)
     return torch.cat(outs, dim=1), torch.cat(lses, dim=2)
+
+
+# ------------------------------------------------------------------------------------------------
+# Fused exchange + merge: every rank reads the other ranks' partials directly from their memory
+# ------------------------------------------------------------------------------------------------
+_P2P_BUFFERS = {}
+
+
+def _p2p_buffers(shape_o, shape_l, dtype, device, group):
+    """Symmetric-memory buffers for the partial (O, LSE) of one problem shape, allocated and exchanged once
+    per (shape, group) and reused.  Returns (o_buf, lse_buf, handle_o, handle_l)."""
+    import torch.distributed._symmetric_memory as symm_mem
+
+    group = group or dist.group.WORLD
+    key = (tuple(shape_o), tuple(shape_l), dtype, str(device), group.group_name)
+    if key not in _P2P_BUFFERS:
+        o_buf = symm_mem.empty(*shape_o, dtype=dtype, device=device)
+        l_buf = symm_mem.empty(*shape_l, dtype=torch.float32, device=device)
+        _P2P_BUFFERS[key] = (o_buf, l_buf, symm_mem.rendezvous(o_buf, group.group_name),
+                             symm_mem.rendezvous(l_buf, group.group_name))
+    return _P2P_BUFFERS[key]
+
+
+def sequence_parallel_forward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor,
+                                  softmax_scale: Optional[float] = None, causal: bool = False,
+                                  group: Optional[dist.ProcessGroup] = None):
+    """Same result as ``sequence_parallel_forward`` (this rank's query-row slice), but without the
+    all-to-all: the partials are written into symmetric memory, a device-side barrier orders the ranks,
+    and ONE kernel (``fa_combine_gather``) reads the query-row slice of every rank's partial straight from
+    that rank's HBM over NVLink (plain loads, no multicast) and merges it.  Needs
+    ``torch.distributed._symmetric_memory``; raises if the peers' memory cannot be mapped."""
+    from . import _ext
+
+    ext = _ext.load()
+    rank = dist.get_rank(group)
+    world = dist.get_world_size(group)
+    b, s, h, d = q.shape
+    if s % world != 0:
+        raise ValueError("seqlen_q must be divisible by the number of ranks")
+    scale = d ** -0.5 if softmax_scale is None else softmax_scale
+    o_buf, l_buf, hdl_o, hdl_l = _p2p_buffers(q.shape, (b, h, s), q.dtype, q.device, group)
+    partial_attention(q, k_shard, v_shard, rank * k_shard.shape[1], scale, causal, None, o_buf, l_buf)
+    hdl_o.barrier(channel=0)  # every rank's partial is complete and visible
+    o_parts = [hdl_o.get_buffer(r, q.shape, q.dtype) for r in range(world)]
+    l_parts = [hdl_l.get_buffer(r, (b, h, s), torch.float32) for r in range(world)]
+    sl = s // world
+    out, lse = ext.combine_gather(o_parts, l_parts, rank * sl, sl)
+    hdl_o.barrier(channel=1)  # nobody overwrites a partial that a peer is still reading
+    return out, lse

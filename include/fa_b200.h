@@ -232,6 +232,31 @@ typedef struct FaCombineParams {
 
 int fa_combine(const FaCombineParams* p, fa_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------- */
+/* Merge of per-rank partial results of a sequence-sharded forward, reading the partials where    */
+/* they are: o_part[r] / lse_part[r] may point into ANOTHER GPU's memory (peer-mapped, e.g. a    */
+/* symmetric-memory buffer); the kernel reads them with ordinary loads over NVLink, so the        */
+/* exchange and the merge are one kernel and no staging copy or all-to-all is needed.  No         */
+/* counterpart in the reference (it has no multi-GPU code); the arithmetic is that of              */
+/* kvcache_combine_kernel (kvcache_native.cu:676-729).                                           */
+/* Partials are in the layout the forward writes: o_part[r] fp16 (b, seqlen_q, h, d) contiguous,  */
+/* lse_part[r] fp32 (b, h, seqlen_q) contiguous, -inf where rank r saw no key.  This call merges  */
+/* query rows [row_begin, row_begin + rows) of every sequence into o (b, rows, h, d) fp16 and     */
+/* lse (b, h, rows) fp32.  The caller orders the call after every rank has finished its partial.   */
+/* ------------------------------------------------------------------------------------------- */
+#define FA_MAX_GATHER_PARTS 16
+typedef struct FaCombineGatherParams {
+  const void* o_part[FA_MAX_GATHER_PARTS];
+  const float* lse_part[FA_MAX_GATHER_PARTS];
+  void* o;
+  float* lse;
+  int32_t num_parts, b, h, seqlen_q, d;
+  int32_t row_begin, rows;
+  int32_t reserved0;
+} FaCombineGatherParams;
+
+int fa_combine_gather(const FaCombineGatherParams* p, fa_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

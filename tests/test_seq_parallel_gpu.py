@@ -40,12 +40,22 @@ def _worker(rank, world, port, causal, d, results):
         vs = v[:, rank * shard:(rank + 1) * shard].contiguous().to(dev)
         out, lse = sp.sequence_parallel_forward(qd, ks, vs, None, causal, gather_output=True)
         torch.cuda.synchronize()
+        # fused exchange + merge over peer memory must give the same slice as the all-to-all path
+        p2p_err = -1.0
+        try:
+            out_p, lse_p = sp.sequence_parallel_forward_p2p(qd, ks, vs, None, causal)
+            torch.cuda.synchronize()
+            sl = s // world
+            p2p_err = max((out_p.float() - out[:, rank * sl:(rank + 1) * sl].float()).abs().max().item(),
+                          (lse_p - lse[:, :, rank * sl:(rank + 1) * sl]).abs().max().item())
+        except (ImportError, RuntimeError) as exc:  # symmetric memory not usable on this box
+            print("p2p path unavailable:", exc)
         ref_out, ref_lse = orc.attention_forward(q, k, v, None, causal)
         one_out, _ = ext.fwd(qd, k.to(dev), v.to(dev), d ** -0.5, causal)
         results[rank] = ((out.float().cpu() - ref_out).abs().max().item(),
                          (lse.cpu() - ref_lse).abs().max().item(),
                          (out.float() - one_out.float()).abs().max().item(),
-                         int(ext.device_status(True)))
+                         int(ext.device_status(True)), p2p_err)
     finally:
         dist.destroy_process_group()
 
@@ -60,7 +70,8 @@ def test_two_gpu_sequence_parallel_forward(causal, d):
     results = mgr.dict()
     mp.spawn(_worker, args=(world, _free_port(), causal, d, results), nprocs=world, join=True)
     for rank in range(world):
-        err_o, err_l, err_one, status = results[rank]
+        err_o, err_l, err_one, status, p2p_err = results[rank]
+        assert p2p_err <= 1e-3, (rank, p2p_err)  # -1 when symmetric memory is unavailable
         assert status == 0
         assert err_o <= 3e-3, (rank, err_o)       # fp16 partials merged: two fp16 roundings
         assert err_l <= 1e-3, (rank, err_l)
