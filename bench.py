@@ -41,6 +41,11 @@ WORKLOAD = dict(b=4, s=8192, h=32, h_k=32, d=128, causal=True)
 DECODE = dict(b=64, h=32, h_k=8, d=128, page=256, pages=16384, max_pages=129, lo=1024, hi=32768)
 METRIC = "attn fwd+bwd TFLOP/s (hd128 causal, S=8k)"
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
+# DRAM bytes (read + write) per launch of the kernels at exactly the workloads above, from one ncu capture
+# (dram__bytes_read.sum + dram__bytes_write.sum, one pass; summary in profiles/dram_traffic_full_size.md).
+# They are constants of the workload, not measured by this script; algorithmic tensor bytes for comparison:
+# forward 1078 MB, backward 3494 MB, decode 4275 MB.
+NCU_TRAFFIC_BYTES = dict(fwd=1058.7e6, bwd=548.3e6 + 1333.3e6 + 1587.6e6, decode=4286.8e6 + 4.5e6)
 
 
 def fwd_flops(b, h, sq, sk, d, causal):
@@ -503,15 +508,16 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     tensor_peak = peaks["bf16_tflops_sustained"]  # kernels timed inside a long loop under the power cap
 
-    def tensor_roofline(flops, ms, kernel):
+    def tensor_roofline(flops, ms, kernel, traffic):
         ach = flops / (ms * 1e-3) / 1e12
         return {"kernel": kernel, "bound": "tensor", "achieved": ach, "peak": tensor_peak, "unit": "TFLOP/s",
-                "frac": ach / tensor_peak, "frac_of_nominal_2250": ach / 2250.0, "traffic": None,
+                "frac": ach / tensor_peak, "frac_of_nominal_2250": ach / 2250.0, "traffic": traffic,
                 "peak_source": f"{peak_src} (cuBLAS bf16 sustained)", "ms_per_launch": ms}
 
-    roofline = tensor_roofline(f_bwd, bwd_ms, "backward: bwd_preprocess + bwd_dq_kernel + bwd_dkdv_kernel (2.5x forward FLOPs)")
+    roofline = tensor_roofline(f_bwd, bwd_ms, "backward: bwd_preprocess + bwd_dq_kernel + bwd_dkdv_kernel (2.5x forward FLOPs)",
+                               NCU_TRAFFIC_BYTES["bwd"])
     roofline["ms_by_kernel"] = {"bwd_preprocess_kernel": pre_ms, "bwd_dq_kernel": dq_ms, "bwd_dkdv_kernel": dkdv_ms}
-    roofline_fwd = tensor_roofline(f_fwd, fwd_ms, "fwd_kernel<128>")
+    roofline_fwd = tensor_roofline(f_fwd, fwd_ms, "fwd_kernel<128>", NCU_TRAFFIC_BYTES["fwd"])
 
     # ---- end to end through the public API, host buffers in and out every step ----
     hq, hk_, hv, hdo = (x.cpu().pin_memory() for x in (q, k, v, dout))
@@ -586,7 +592,7 @@ def main():
         per_gpu = best[1] / world
         roofline_decode = {"kernel": "decode_kernel<128> + combine_kernel<128> + append_kernel", "bound": "hbm",
                            "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": per_gpu / peaks["hbm_gbs"],
-                           "frac_of_nominal_8000": per_gpu / 8000.0, "traffic": None, "num_splits": best[0],
+                           "frac_of_nominal_8000": per_gpu / 8000.0, "traffic": NCU_TRAFFIC_BYTES["decode"], "num_splits": best[0],
                            "peak_source": f"{peak_src} (copy bandwidth)", "ms_per_launch": best[2]}
         status |= lib.fa_device_status(1)
         del kc, vc
