@@ -5,18 +5,22 @@
 //                   per (b, h); padded rows get -lse2 = -inf so that they produce P = 0.
 //   2. dQ kernel    one CTA per 128-row Q tile; loops over K/V blocks:
 //                     S  = Q K_j^T, dP = dO V_j^T            (tcgen05 SS, fp32 in TMEM)
-//                     P  = exp2(S*c - lse2), dS = P o (dP - delta) -> fp16, written back into TMEM
+//                     P  = exp2(S*c - lse2), dS = P o (dP - delta) -> fp16, written to TMEM columns of its own
 //                     dQ += dS K_j                            (tcgen05 TS, K_j as MN-major B operand)
 //   3. dK/dV kernel one CTA per 128-key tile of one KV head; loops over the query heads of the GQA
 //                   group and their Q tiles, accumulating in TMEM (fp32) so that dK/dV are written
 //                   once per KV head:
 //                     S^T = K Q_i^T, dP^T = V dO_i^T          (SS)
-//                     P^T, dS^T -> fp16 in TMEM (aliased onto S^T / dP^T)
+//                     P^T, dS^T -> fp16 in TMEM columns of their own
 //                     dV += P^T dO_i, dK += dS^T Q_i          (TS, dO_i / Q_i as MN-major B operands)
-// Warp roles in kernels 2 and 3 (576 threads): warps 0-15 elementwise math (four threads per TMEM lane,
-// each owning 32 of the 128 columns of a tile), warp 16 TMA producer, warp 17 MMA issuer.
-// TMEM columns: dQ kernel S [0,128) dP [128,256) dQ [256,256+D); dK/dV kernel S^T [0,128)
-// dP^T [128,256) dV [256,256+D) dK [256+D,256+2D).
+// Warp roles in kernels 2 and 3 (608 threads): warps 0-15 elementwise math (four threads per TMEM lane,
+// each owning 32 of the 128 columns of a tile), warp 16 TMA producer, warp 17 issues the SS products
+// that feed the elementwise warps, warp 18 the accumulating TS products.
+// TMEM columns.  dQ kernel: S [0,128), dP [128,256), dQ [256,256+D), packed dS double-buffered in
+// [384,448) / [448,512).  dK/dV kernel: one 128-column accumulator region A [0,128) that holds S^T and
+// then dP^T of the same Q tile in turn, packed P^T [128,192) and dS^T [192,256), dV [256,256+D),
+// dK [256+D,256+2D).  A region is handed back to the MMA warp as soon as its values sit in registers, so
+// the next S / dP / S^T is computed while the elementwise warps are still busy with the current tile.
 //
 // Replaces flash_bwd_dot_do_o_kernel (csrc/flash_attn/src/flash_bwd_preprocess_kernel.h:23-96),
 // compute_dq_1rowblock and compute_dk_dv_1colblock (src/flash_bwd_kernel.h:25-609, 613-1344) and
@@ -28,14 +32,16 @@ namespace fa {
 namespace {
 
 constexpr int kBlock = 128;  // tile edge in both sequence dimensions
-constexpr int kNumThreads = 576;
+constexpr int kNumThreads = 608;  // 16 elementwise warps, TMA producer, two MMA-issuing warps
 constexpr int kComputeWarps = 16;
 constexpr int kProducerWarp = 16;
-constexpr int kMmaWarp = 17;
+constexpr int kMmaWarp = 17;    // issues the products S, dP (S^T, dP^T) that feed the elementwise warps
+constexpr int kAccMmaWarp = 18; // issues the accumulating products dQ (dV, dK)
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0;
 constexpr int kColDP = 128;
 constexpr int kColAcc = 256;
+constexpr int kColPacked = 384;  // dQ kernel: packed dS, two buffers of 64 columns
 __device__ __forceinline__ float2 exp2_pair(float2 x) { return make_float2(ex2f(x.x), ex2f(x.y)); }
 
 struct BwdKernelParams {
@@ -63,8 +69,22 @@ struct BCfg {
   static constexpr int kChunkBytes = 128 * 128;
   static constexpr int kTileBytes = kChunks * kChunkBytes;
   static constexpr int kStages = (D == 128) ? 2 : 3;
-  static constexpr int kSmemBytes = 2 * kTileBytes + 2 * kStages * kTileBytes + 4096 /*stats*/ +
-                                    1024 /*barriers*/ + 1024 /*alignment*/;
+  // dQ kernel: a K tile lives from the S MMAs of its block to the dQ MMAs one block later, a V tile only
+  // for the dP MMAs, so K gets one stage more (3 x 32 KB + 2 x 32 KB + Q + dO = 224 KB at D = 128).
+  static constexpr int kStagesK = kStages + 1;
+  static constexpr int kStagesV = kStages;
+  static constexpr int kSmemBytesDq = 2 * kTileBytes + (kStagesK + kStagesV) * kTileBytes + 512 /*barriers*/ +
+                                      1024 /*alignment*/;
+  // dK/dV kernel: a Q tile lives from the S^T MMAs of its iteration to the dK MMAs issued one iteration
+  // later, a dO tile for less than one iteration; the row statistics have a ring of their own (2 x 1 KB)
+  // that the elementwise warps release.  At D = 128 the tiles take 224 KB, which leaves no room for an
+  // alignment pad: the kernel checks that the dynamic shared memory starts on a 1024-byte boundary.
+  static constexpr int kStagesQ = kStages + 1;
+  static constexpr int kStagesDO = kStages;
+  static constexpr int kAlignPadDkdv = (D == 128) ? 0 : 1024;
+  static constexpr int kSmemBytesDkdv = 2 * kTileBytes + (kStagesQ + kStagesDO) * kTileBytes + 2048 /*stats*/ +
+                                        512 /*barriers*/ + kAlignPadDkdv;
+  static_assert(kSmemBytesDq <= 227 * 1024 && kSmemBytesDkdv <= 227 * 1024, "shared memory budget");
 };
 
 struct BBarriers {
@@ -75,38 +95,46 @@ struct BBarriers {
   uint64_t b_empty[4];
   uint64_t s_full;         // S (or S^T) accumulator ready
   uint64_t dp_full;        // dP (or dP^T) accumulator ready
-  uint64_t p_full[2];      // P^T written to TMEM (dK/dV kernel), first / second 16 columns of every quarter
-  uint64_t ds_full[2];     // dS (or dS^T) written to TMEM, likewise in two steps
-  uint64_t s_free;         // S has been read into registers (dQ kernel): the next S may be issued
+  uint64_t p_full;         // packed P^T written to TMEM (dK/dV kernel)
+  uint64_t ds_full;        // packed dS (or dS^T) written to TMEM
+  uint64_t s_loaded;       // S (S^T) sits in registers: its TMEM region may be overwritten
+  uint64_t dp_loaded;      // dP (dP^T) sits in registers
+  uint64_t p_free;         // dV MMAs of the previous tile have consumed the packed P^T
+  uint64_t ds_free[2];     // dK/dV kernel [0]: dK MMAs of the previous tile have consumed the packed dS^T;
+                           // dQ kernel [u]: the dQ MMAs have consumed packed-dS buffer u
+  uint64_t st_full[2];     // dK/dV kernel: row statistics (lse, delta) of a Q tile loaded
+  uint64_t st_empty[2];    // ... and read by all elementwise warps
   uint64_t acc_full;       // final accumulators ready
   uint32_t tmem_base;
   int abort_flag;
 };
 
-__device__ __forceinline__ void init_barriers(BBarriers* bars, int stages) {
+// a_users / b_users: how many MMA-issuing threads read the tiles of ring A / B (each commits on "empty").
+__device__ __forceinline__ void init_barriers(BBarriers* bars, int stages, int a_users, int b_users) {
   mbar_init(&bars->fixed_full, 1);
   for (int s = 0; s < stages; ++s) {
     mbar_init(&bars->a_full[s], 1);
-    mbar_init(&bars->a_empty[s], 1);
+    mbar_init(&bars->a_empty[s], a_users);
     mbar_init(&bars->b_full[s], 1);
-    mbar_init(&bars->b_empty[s], 1);
+    mbar_init(&bars->b_empty[s], b_users);
   }
   mbar_init(&bars->s_full, 1);
   mbar_init(&bars->dp_full, 1);
-  for (int c = 0; c < 2; ++c) {
-    mbar_init(&bars->p_full[c], kComputeWarps);
-    mbar_init(&bars->ds_full[c], kComputeWarps);
+  mbar_init(&bars->p_full, kComputeWarps);
+  mbar_init(&bars->ds_full, kComputeWarps);
+  mbar_init(&bars->s_loaded, kComputeWarps);
+  mbar_init(&bars->dp_loaded, kComputeWarps);
+  for (int i = 0; i < 2; ++i) {
+    mbar_init(&bars->st_full[i], 1);
+    mbar_init(&bars->st_empty[i], kComputeWarps);
   }
-  mbar_init(&bars->s_free, kComputeWarps);
+  mbar_init(&bars->p_free, 1);
+  mbar_init(&bars->ds_free[0], 1);
+  mbar_init(&bars->ds_free[1], 1);
   mbar_init(&bars->acc_full, 1);
   bars->abort_flag = 0;
   fence_mbar_init();
 }
-
-// TMEM column of the packed-fp16 A slice k (16 elements = 8 columns) inside a 128-column fp32 region
-// whose four 32-column quarters are owned by different threads: each quarter holds its 32 packed
-// values (two slices) in its own first 16 columns.
-__device__ __forceinline__ uint32_t packed_slice_col(int k) { return (k >> 1) * 32 + (k & 1) * 8; }
 
 // Tile descriptors (built once per tile by the MMA thread) and their K=16 slices.
 // K-major 128-row tile: slice k lives in swizzle chunk k/4 at byte (k%4)*32 inside the 128-byte row.
@@ -123,28 +151,56 @@ __device__ __forceinline__ uint64_t kmajor_slice(uint64_t tile_desc, int k) {
 }
 __device__ __forceinline__ uint64_t mnmajor_slice(uint64_t tile_desc, int k) { return desc_advance(tile_desc, k * 2048); }
 
-// C (+)= A[smem, K-major] * B[smem, K-major]^T over D, both 128-row tiles.
-template <int D>
-__device__ __forceinline__ void gemm_ss(uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile, uint32_t idesc) {
+// A thread that issues tcgen05.mma is held for the duration of each MMA (about 66 clocks for
+// 128x128x16), and whatever else it executes -- a barrier poll costs 60-80 clocks even when the barrier
+// completed long ago, a commit about 50 -- is time in which it feeds nothing to the tensor pipe.  Two
+// measures keep the pipe busy: the products are issued by two warps (kMmaWarp, kAccMmaWarp), so that one
+// polls while the other issues, and a product takes a hook that runs after half of its MMAs for waits on
+// TMA loads of the NEXT product, which are satisfied long before and cost only the poll.  A hook returns
+// false when a bounded wait gave up; the rest of the product is then skipped.
+// C = A[smem, K-major] * B[smem, K-major]^T over D, both 128-row tiles.
+template <int D, class Hook>
+__device__ __forceinline__ bool gemm_ss(uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile, uint32_t idesc,
+                                        Hook hook) {
   const uint64_t ad = kmajor_tile<D>(a_tile), bd = kmajor_tile<D>(b_tile);
+  constexpr int kSlices = D / 16;
 #pragma unroll
-  for (int k = 0; k < D / 16; ++k) mma_ss(d_tmem, kmajor_slice<D>(ad, k), kmajor_slice<D>(bd, k), idesc, k > 0);
+  for (int k = 0; k < kSlices; ++k) {
+    if (k == kSlices / 2 && !hook()) return false;
+    mma_ss(d_tmem, kmajor_slice<D>(ad, k), kmajor_slice<D>(bd, k), idesc, k > 0);
+  }
+  return true;
 }
-// C (+)= A[tmem, packed fp16] * B[smem tile used MN-major, N = D] over the four K=16 slices {c, c+2, c+4,
-// c+6} (c = 0 or 1): the slices the elementwise threads hand over in their first / second step.
+// C (+)= A[tmem, 128 packed fp16 contraction elements in 64 consecutive columns] * B[smem tile used
+// MN-major, N = D].
 template <int D>
-__device__ __forceinline__ void gemm_ts_half(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_tile, uint32_t idesc, int c,
-                                             bool zero_init) {
+__device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_tile, uint32_t idesc,
+                                        bool zero_init) {
   const uint64_t bd = mnmajor_tile<D>(b_tile);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int k = 2 * i + c;
-    mma_ts(d_tmem, a_tmem + packed_slice_col(k), mnmajor_slice(bd, k), idesc, (zero_init && i == 0) ? 0u : 1u);
-  }
+  for (int k = 0; k < 8; ++k)
+    mma_ts(d_tmem, a_tmem + k * 8, mnmajor_slice(bd, k), idesc, (zero_init && k == 0) ? 0u : 1u);
 }
+
 // One warp's arrival on a barrier that counts warps: all lanes have finished their TMEM stores.
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   tmem_wait_st();
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+// A poll of a barrier costs the elementwise warps 100-170 clocks even when it completed long ago, so the
+// barriers that normally complete early are probed ahead of time, with independent work (a TMEM load,
+// the arithmetic of a phase) between the probe and its use; the blocking wait runs only if the probe
+// failed.  The vote makes the result uniform over the warp.
+__device__ __forceinline__ bool warp_probe(uint64_t* bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, mbar_test_nonblocking(bar, parity) != 0);
+}
+__device__ __forceinline__ bool warp_wait_unless(bool probed, uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
+  return probed || mbar_wait_warp(bar, parity, ctx);
+}
+// The same after TMEM loads (tcgen05.wait::ld already executed): the region may be overwritten.
+__device__ __forceinline__ void warp_arrive_loaded(uint64_t* bar, int lane) {
   tc_fence_before_sync();
   __syncwarp();
   if (lane == 0) mbar_arrive(bar);
@@ -252,11 +308,11 @@ bwd_dq_kernel(const __grid_constant__ BwdKernelParams p) {
   uint8_t* sQ = smem;
   uint8_t* sdO = sQ + C::kTileBytes;
   uint8_t* sK = sdO + C::kTileBytes;
-  uint8_t* sV = sK + C::kStages * C::kTileBytes;
-  BBarriers* bars = reinterpret_cast<BBarriers*>(sV + C::kStages * C::kTileBytes + 4096);
+  uint8_t* sV = sK + C::kStagesK * C::kTileBytes;
+  BBarriers* bars = reinterpret_cast<BBarriers*>(sV + C::kStagesV * C::kTileBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  if (threadIdx.x == 0) init_barriers(bars, C::kStages);
+  if (threadIdx.x == 0) init_barriers(bars, C::kStagesK, 2, 1);
   if (warp == kMmaWarp) {
     tmem_alloc(&bars->tmem_base, kTmemCols);
     tmem_relinquish();
@@ -276,8 +332,8 @@ bwd_dq_kernel(const __grid_constant__ BwdKernelParams p) {
         tma_load_4d(sdO + c * C::kChunkBytes, &p.tm_do, &bars->fixed_full, c * 64, head, q_off + row0, bq);
       }
       for (int j = 0; j < nb; ++j) {
-        const int s = j % C::kStages;
-        const uint32_t ph = (j / C::kStages) & 1;
+        const int s = j % C::kStagesK, sv = j % C::kStagesV;
+        const uint32_t ph = (j / C::kStagesK) & 1, phv = (j / C::kStagesV) & 1;
         const int krow = k_off + j * kBlock;
         if (!mbar_wait(&bars->a_empty[s], ph ^ 1, ctx)) break;
         mbar_arrive_expect_tx(&bars->a_full[s], C::kTileBytes);
@@ -285,65 +341,59 @@ bwd_dq_kernel(const __grid_constant__ BwdKernelParams p) {
         for (int c = 0; c < C::kChunks; ++c)
           tma_load_4d(sK + s * C::kTileBytes + c * C::kChunkBytes, &p.tm_k, &bars->a_full[s], c * 64, head_k,
                       krow, bq);
-        if (!mbar_wait(&bars->b_empty[s], ph ^ 1, ctx)) break;
-        mbar_arrive_expect_tx(&bars->b_full[s], C::kTileBytes);
+        if (!mbar_wait(&bars->b_empty[sv], phv ^ 1, ctx)) break;
+        mbar_arrive_expect_tx(&bars->b_full[sv], C::kTileBytes);
 #pragma unroll
         for (int c = 0; c < C::kChunks; ++c)
-          tma_load_4d(sV + s * C::kTileBytes + c * C::kChunkBytes, &p.tm_v, &bars->b_full[s], c * 64, head_k,
+          tma_load_4d(sV + sv * C::kTileBytes + c * C::kChunkBytes, &p.tm_v, &bars->b_full[sv], c * 64, head_k,
                       krow, bq);
       }
     }
   } else if (warp == kMmaWarp) {
     if (lane == 0 && nb > 0) {
       constexpr uint32_t idesc_nn = make_idesc_f16(128, kBlock, false, false);
-      constexpr uint32_t idesc_acc = make_idesc_f16(128, D, false, true);
       const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO);
-      // Issue order per block j:  [S(j+1) as soon as S(j) sits in registers]  dQ(j)  dP(j+1).
-      // dS(j) lives in the dP region, so S(j+1) may overwrite the S region early and runs under the
-      // elementwise phase of block j; dP(j+1) follows dQ(j) in the (in-order) tensor pipe.
-      auto issue_s = [&](int j) {
-        const int s = j % C::kStages;
-        gemm_ss<D>(tmem_base + kColS, q_addr, smem_u32(sK + s * C::kTileBytes), idesc_nn);
-        tc_commit(&bars->s_full);
-      };
-      auto issue_dp = [&](int j) {
-        const int s = j % C::kStages;
-        gemm_ss<D>(tmem_base + kColDP, do_addr, smem_u32(sV + s * C::kTileBytes), idesc_nn);
-        tc_commit(&bars->dp_full);
-        tc_commit(&bars->b_empty[s]);
-      };
-      bool ok = mbar_wait(&bars->fixed_full, 0, ctx);
-      if (ok) ok = mbar_wait(&bars->a_full[0], 0, ctx);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_s(0);
-        ok = mbar_wait(&bars->b_full[0], 0, ctx);
-      }
-      if (ok) {
-        tc_fence_after_sync();
-        issue_dp(0);
-      }
+      // S(j+1) is issued as soon as S(j) sits in registers and dP(j+1) as soon as dP(j) does, so both run
+      // under the elementwise work of block j.  The hooks wait for the TMA load the next product reads.
+      auto wait = [&](uint64_t* bar, uint32_t parity) { return mbar_wait(bar, parity, ctx); };
+      auto k_tile = [&](int j) { return smem_u32(sK + (j % C::kStagesK) * C::kTileBytes); };
+      auto v_tile = [&](int j) { return smem_u32(sV + (j % C::kStagesV) * C::kTileBytes); };
+      auto k_full = [&](int j) { return wait(&bars->a_full[j % C::kStagesK], (j / C::kStagesK) & 1); };
+      auto v_full = [&](int j) { return wait(&bars->b_full[j % C::kStagesV], (j / C::kStagesV) & 1); };
+      bool ok = wait(&bars->fixed_full, 0) && k_full(0);
       for (int j = 0; ok && j < nb; ++j) {
-        const int s = j % C::kStages;
-        const int s1 = (j + 1) % C::kStages;
-        const uint32_t ph1 = ((j + 1) / C::kStages) & 1;
-        const uint32_t k_addr = smem_u32(sK + s * C::kTileBytes);
-        // TMA barriers of the next block complete early: pass them before the critical hand-offs
-        if (j + 1 < nb) {
-          if (!(ok = mbar_wait(&bars->a_full[s1], ph1, ctx))) break;
-          if (!(ok = mbar_wait(&bars->b_full[s1], ph1, ctx))) break;
-          if (!(ok = mbar_wait(&bars->s_free, j & 1, ctx))) break;
-          tc_fence_after_sync();
-          issue_s(j + 1);
-        }
-        if (!(ok = mbar_wait(&bars->ds_full[0], j & 1, ctx))) break;
+        if (j > 0 && !(ok = wait(&bars->s_loaded, (j - 1) & 1))) break;
+        // S(j) complete tells the elementwise warps that packed-dS buffer j&1 is free again
+        if (j >= 2 && !(ok = wait(&bars->ds_free[j & 1], ((j >> 1) - 1) & 1))) break;
         tc_fence_after_sync();
-        gemm_ts_half<D>(tmem_base + kColAcc, tmem_base + kColDP, k_addr, idesc_acc, 0, j == 0);
-        if (!(ok = mbar_wait(&bars->ds_full[1], j & 1, ctx))) break;
+        ok = gemm_ss<D>(tmem_base + kColS, q_addr, k_tile(j), idesc_nn, [&] { return v_full(j); });
+        if (!ok) break;
+        tc_commit(&bars->s_full);
+        tc_commit(&bars->a_empty[j % C::kStagesK]);  // second reader: the dQ MMAs of this block
+        if (j > 0 && !(ok = wait(&bars->dp_loaded, (j - 1) & 1))) break;
         tc_fence_after_sync();
-        gemm_ts_half<D>(tmem_base + kColAcc, tmem_base + kColDP, k_addr, idesc_acc, 1, false);
+        ok = gemm_ss<D>(tmem_base + kColDP, do_addr, v_tile(j), idesc_nn,
+                        [&] { return j + 1 >= nb || k_full(j + 1); });
+        if (!ok) break;
+        tc_commit(&bars->dp_full);
+        tc_commit(&bars->b_empty[j % C::kStagesV]);
+      }
+    }
+  } else if (warp == kAccMmaWarp) {
+    if (lane == 0 && nb > 0) {
+      // dQ += dS(j) K(j) as soon as the packed dS(j) is written.  dS has two buffers; ds_free[u] tells the
+      // elementwise warps that buffer u has been consumed.
+      constexpr uint32_t idesc_acc = make_idesc_f16(128, D, false, true);
+      bool ok = true;
+      for (int j = 0; ok && j < nb; ++j) {
+        const int s = j % C::kStagesK;
+        if (!(ok = mbar_wait(&bars->a_full[s], (j / C::kStagesK) & 1, ctx))) break;
+        if (!(ok = mbar_wait(&bars->ds_full, j & 1, ctx))) break;
+        tc_fence_after_sync();
+        gemm_ts<D>(tmem_base + kColAcc, tmem_base + kColPacked + (j & 1) * 64, smem_u32(sK + s * C::kTileBytes),
+                   idesc_acc, j == 0);
         tc_commit(&bars->a_empty[s]);
-        if (j + 1 < nb) issue_dp(j + 1);
+        tc_commit(&bars->ds_free[j & 1]);
       }
       if (ok) tc_commit(&bars->acc_full);
     }
@@ -361,15 +411,15 @@ bwd_dq_kernel(const __grid_constant__ BwdKernelParams p) {
     const float c = p.scale_log2;
     const float2 c2 = make_float2(c, c), nl2 = make_float2(neg_lse2, neg_lse2), nd2 = make_float2(neg_delta, neg_delta);
     bool ok = true;
+    bool s_ready = false;  // probe of s_full for the coming block
     for (int j = 0; j < nb; ++j) {
-      if (!(ok = mbar_wait_warp(&bars->s_full, j & 1, ctx))) break;
+      if (!(ok = warp_wait_unless(s_ready, &bars->s_full, j & 1, ctx))) break;
       tc_fence_after_sync();
       uint32_t sr[32];
       tmem_ld32(tS, sr);
+      const bool dp_ready = warp_probe(&bars->dp_full, j & 1);  // dP(j) follows S(j) through the pipe
       tmem_wait_ld();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->s_free);
+      warp_arrive_loaded(&bars->s_loaded, lane);
       const int col0 = j * kBlock + cq * 32;
       int limit = sk - 1 - col0;
       if (p.is_causal) limit = min(limit, row + sk - sq - col0);
@@ -386,23 +436,22 @@ bwd_dq_kernel(const __grid_constant__ BwdKernelParams p) {
           if (2 * i + 1 > limit) pr[i].y = 0.f;
         }
       }
-      if (!(ok = mbar_wait_warp(&bars->dp_full, j & 1, ctx))) break;
+      if (!(ok = warp_wait_unless(dp_ready, &bars->dp_full, j & 1, ctx))) break;
       tc_fence_after_sync();
       tmem_ld32(tDP, sr);
+      s_ready = j + 1 < nb && warp_probe(&bars->s_full, (j + 1) & 1);  // S(j+1) ran under the exponentials
       tmem_wait_ld();
-      // packed dS of this quarter -> first 16 columns of the quarter of the dP region, in two steps of 8
+      warp_arrive_loaded(&bars->dp_loaded, lane);
+      uint32_t pk[16];
 #pragma unroll
-      for (int c8 = 0; c8 < 2; ++c8) {
-        uint32_t pk[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int e = c8 * 8 + i;
-          const float2 d = fmul2(pr[e], fadd2(make_float2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1])), nd2));
-          pk[i] = pack_half2(d.x, d.y);
-        }
-        tmem_st8(tDP + c8 * 8, pk);
-        warp_arrive(&bars->ds_full[c8], lane);
+      for (int i = 0; i < 16; ++i) {
+        const float2 d = fmul2(pr[i], fadd2(make_float2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1])), nd2));
+        pk[i] = pack_half2(d.x, d.y);
       }
+      // packed dS: 64 consecutive columns per block (16 per column quarter), two alternating buffers; the
+      // buffer is free because S(j) was issued only after the dQ MMAs of block j-2 had consumed it
+      tmem_st16(tmem_base + lane_base + kColPacked + (j & 1) * 64 + cq * 16, pk);
+      warp_arrive(&bars->ds_full, lane);
     }
     // ---- epilogue: dQ = scale * acc; D/32 of the 16 warps-per-lane-quarter groups store 32 columns each ----
     const bool stores = cq < D / 32;
@@ -446,7 +495,7 @@ template <int D>
 __global__ void __launch_bounds__(kNumThreads, 1)
 bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
   using C = BCfg<D>;
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int batch = blockIdx.z, head_k = blockIdx.y, nblk = blockIdx.x;
   const bool varlen = p.cu_seqlens_q != nullptr;
   const int q_off = varlen ? p.cu_seqlens_q[batch] : 0;
@@ -472,12 +521,17 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
   uint8_t* sK = smem;
   uint8_t* sV = sK + C::kTileBytes;
   uint8_t* sQ = sV + C::kTileBytes;
-  uint8_t* sdO = sQ + C::kStages * C::kTileBytes;
-  float* sStats = reinterpret_cast<float*>(sdO + C::kStages * C::kTileBytes);  // [stage][lse2 128 | delta 128]
-  BBarriers* bars = reinterpret_cast<BBarriers*>(reinterpret_cast<uint8_t*>(sStats) + 4096);
+  uint8_t* sdO = sQ + C::kStagesQ * C::kTileBytes;
+  float* sStats = reinterpret_cast<float*>(sdO + C::kStagesDO * C::kTileBytes);  // [2][lse2 128 | delta 128]
+  BBarriers* bars = reinterpret_cast<BBarriers*>(reinterpret_cast<uint8_t*>(sStats) + 2048);
+  static_assert(sizeof(BBarriers) <= 512, "barrier block");
+  if (smem - smem_raw > C::kAlignPadDkdv) {  // uniform over the CTA: nothing has been set up yet
+    if (threadIdx.x == 0 && p.status) atomicOr(p.status, kStatusSmemLayout);
+    return;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  if (threadIdx.x == 0) init_barriers(bars, C::kStages);
+  if (threadIdx.x == 0) init_barriers(bars, C::kStagesQ, 2, 2);
   if (warp == kMmaWarp) {
     tmem_alloc(&bars->tmem_base, kTmemCols);
     tmem_relinquish();
@@ -497,84 +551,81 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
         tma_load_4d(sV + c * C::kChunkBytes, &p.tm_v, &bars->fixed_full, c * 64, head_k, k_off + key0, bq);
       }
       for (int it = 0; it < n_it; ++it) {
-        const int s = it % C::kStages;
-        const uint32_t ph = (it / C::kStages) & 1;
+        const int sq_ = it % C::kStagesQ, sd = it % C::kStagesDO, ss = it & 1;
+        const uint32_t phq = (it / C::kStagesQ) & 1, phd = (it / C::kStagesDO) & 1, phs = (it >> 1) & 1;
         const int head = head_k * group + it / per_head;
         const int i = i_min + it % per_head;
         const int qrow = q_off + i * kBlock;
         const int64_t stat = (static_cast<int64_t>(batch) * p.h + head) * p.sq_pad + i * kBlock;
-        if (!mbar_wait(&bars->a_empty[s], ph ^ 1, ctx)) break;
-        mbar_arrive_expect_tx(&bars->a_full[s], C::kTileBytes + 1024);
+        if (!mbar_wait(&bars->a_empty[sq_], phq ^ 1, ctx)) break;
+        mbar_arrive_expect_tx(&bars->a_full[sq_], C::kTileBytes);
 #pragma unroll
         for (int c = 0; c < C::kChunks; ++c)
-          tma_load_4d(sQ + s * C::kTileBytes + c * C::kChunkBytes, &p.tm_q, &bars->a_full[s], c * 64, head,
+          tma_load_4d(sQ + sq_ * C::kTileBytes + c * C::kChunkBytes, &p.tm_q, &bars->a_full[sq_], c * 64, head,
                       qrow, bq);
-        bulk_load_1d(sStats + s * 256, p.lse2 + stat, 512, &bars->a_full[s]);
-        bulk_load_1d(sStats + s * 256 + 128, p.delta + stat, 512, &bars->a_full[s]);
-        if (!mbar_wait(&bars->b_empty[s], ph ^ 1, ctx)) break;
-        mbar_arrive_expect_tx(&bars->b_full[s], C::kTileBytes);
+        if (!mbar_wait(&bars->st_empty[ss], phs ^ 1, ctx)) break;
+        mbar_arrive_expect_tx(&bars->st_full[ss], 1024);
+        bulk_load_1d(sStats + ss * 256, p.lse2 + stat, 512, &bars->st_full[ss]);
+        bulk_load_1d(sStats + ss * 256 + 128, p.delta + stat, 512, &bars->st_full[ss]);
+        if (!mbar_wait(&bars->b_empty[sd], phd ^ 1, ctx)) break;
+        mbar_arrive_expect_tx(&bars->b_full[sd], C::kTileBytes);
 #pragma unroll
         for (int c = 0; c < C::kChunks; ++c)
-          tma_load_4d(sdO + s * C::kTileBytes + c * C::kChunkBytes, &p.tm_do, &bars->b_full[s], c * 64, head,
+          tma_load_4d(sdO + sd * C::kTileBytes + c * C::kChunkBytes, &p.tm_do, &bars->b_full[sd], c * 64, head,
                       qrow, bq);
       }
     }
   } else if (warp == kMmaWarp) {
     if (lane == 0 && n_it > 0) {
       constexpr uint32_t idesc_nn = make_idesc_f16(128, kBlock, false, false);
-      constexpr uint32_t idesc_acc = make_idesc_f16(128, D, false, true);
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-      // Issue order per Q tile `it`:  dV(it)  S^T(it+1)  dK(it)  dP^T(it+1): the tensor pipe executes in
-      // order, so S^T(it+1) may overwrite the P^T(it) that dV(it) has just consumed and runs under the dS
-      // phase of tile `it`; likewise dP^T(it+1) follows dK(it).
-      auto issue_st = [&](int it) {
-        const uint32_t q_addr = smem_u32(sQ + (it % C::kStages) * C::kTileBytes);
-        gemm_ss<D>(tmem_base + kColS, k_addr, q_addr, idesc_nn);  // S^T = K Q^T
-        tc_commit(&bars->s_full);
-      };
-      auto issue_dpt = [&](int it) {
-        const uint32_t do_addr = smem_u32(sdO + (it % C::kStages) * C::kTileBytes);
-        gemm_ss<D>(tmem_base + kColDP, v_addr, do_addr, idesc_nn);  // dP^T = V dO^T
-        tc_commit(&bars->dp_full);
-      };
-      bool ok = mbar_wait(&bars->fixed_full, 0, ctx);
-      if (ok) ok = mbar_wait(&bars->a_full[0], 0, ctx);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_st(0);
-        ok = mbar_wait(&bars->b_full[0], 0, ctx);
-      }
-      if (ok) {
-        tc_fence_after_sync();
-        issue_dpt(0);
-      }
+      // One accumulator region A holds S^T(it) and then dP^T(it): dP^T(it) is issued as soon as S^T(it)
+      // sits in registers, S^T(it+1) as soon as dP^T(it) does.  The hooks wait for the TMA load the next
+      // product reads.
+      auto wait = [&](uint64_t* bar, uint32_t parity) { return mbar_wait(bar, parity, ctx); };
+      auto q_tile = [&](int it) { return smem_u32(sQ + (it % C::kStagesQ) * C::kTileBytes); };
+      auto do_tile = [&](int it) { return smem_u32(sdO + (it % C::kStagesDO) * C::kTileBytes); };
+      auto q_full = [&](int it) { return wait(&bars->a_full[it % C::kStagesQ], (it / C::kStagesQ) & 1); };
+      auto do_full = [&](int it) { return wait(&bars->b_full[it % C::kStagesDO], (it / C::kStagesDO) & 1); };
+      const uint32_t tA = tmem_base + kColS;
+      bool ok = wait(&bars->fixed_full, 0) && q_full(0);
       for (int it = 0; ok && it < n_it; ++it) {
-        const int s = it % C::kStages;
-        const int s1 = (it + 1) % C::kStages;
-        const uint32_t ph1 = ((it + 1) / C::kStages) & 1;
-        const uint32_t q_addr = smem_u32(sQ + s * C::kTileBytes);
-        const uint32_t do_addr = smem_u32(sdO + s * C::kTileBytes);
-        // TMA barriers of the next tile complete early: pass them before the critical hand-offs
-        if (it + 1 < n_it) {
-          if (!(ok = mbar_wait(&bars->a_full[s1], ph1, ctx))) break;
-          if (!(ok = mbar_wait(&bars->b_full[s1], ph1, ctx))) break;
-        }
-        if (!(ok = mbar_wait(&bars->p_full[0], it & 1, ctx))) break;
+        if (it > 0 && !(ok = wait(&bars->dp_loaded, (it - 1) & 1))) break;
         tc_fence_after_sync();
-        gemm_ts_half<D>(tmem_base + kColAcc, tmem_base + kColS, do_addr, idesc_acc, 0, it == 0);  // dV += P^T dO
-        if (!(ok = mbar_wait(&bars->p_full[1], it & 1, ctx))) break;
+        ok = gemm_ss<D>(tA, k_addr, q_tile(it), idesc_nn, [&] { return do_full(it); });  // S^T(it) = K Q^T
+        if (!ok) break;
+        tc_commit(&bars->s_full);
+        tc_commit(&bars->a_empty[it % C::kStagesQ]);  // second reader: the dK MMAs of this tile
+        if (!(ok = wait(&bars->s_loaded, it & 1))) break;
         tc_fence_after_sync();
-        gemm_ts_half<D>(tmem_base + kColAcc, tmem_base + kColS, do_addr, idesc_acc, 1, false);
-        tc_commit(&bars->b_empty[s]);
-        if (it + 1 < n_it) issue_st(it + 1);
-        if (!(ok = mbar_wait(&bars->ds_full[0], it & 1, ctx))) break;
+        ok = gemm_ss<D>(tA, v_addr, do_tile(it), idesc_nn,  // dP^T(it) = V dO^T
+                        [&] { return it + 1 >= n_it || q_full(it + 1); });
+        if (!ok) break;
+        tc_commit(&bars->dp_full);
+        tc_commit(&bars->b_empty[it % C::kStagesDO]);  // second reader: the dV MMAs of this tile
+      }
+    }
+  } else if (warp == kAccMmaWarp) {
+    if (lane == 0 && n_it > 0) {
+      // dV += P^T(it) dO(it) as soon as the packed P^T is written, dK += dS^T(it) Q(it) likewise.
+      constexpr uint32_t idesc_acc = make_idesc_f16(128, D, false, true);
+      const uint32_t tP = tmem_base + kColDP, tDS = tmem_base + kColDP + 64;
+      const uint32_t tDV = tmem_base + kColAcc, tDK = tmem_base + kColAcc + D;
+      bool ok = true;
+      for (int it = 0; ok && it < n_it; ++it) {
+        const int sq_ = it % C::kStagesQ, sd = it % C::kStagesDO;
+        if (!(ok = mbar_wait(&bars->b_full[sd], (it / C::kStagesDO) & 1, ctx))) break;
+        if (!(ok = mbar_wait(&bars->p_full, it & 1, ctx))) break;
         tc_fence_after_sync();
-        gemm_ts_half<D>(tmem_base + kColAcc + D, tmem_base + kColDP, q_addr, idesc_acc, 0, it == 0);  // dK += dS^T Q
-        if (!(ok = mbar_wait(&bars->ds_full[1], it & 1, ctx))) break;
+        gemm_ts<D>(tDV, tP, smem_u32(sdO + sd * C::kTileBytes), idesc_acc, it == 0);
+        tc_commit(&bars->b_empty[sd]);
+        tc_commit(&bars->p_free);
+        if (!(ok = mbar_wait(&bars->a_full[sq_], (it / C::kStagesQ) & 1, ctx))) break;
+        if (!(ok = mbar_wait(&bars->ds_full, it & 1, ctx))) break;
         tc_fence_after_sync();
-        gemm_ts_half<D>(tmem_base + kColAcc + D, tmem_base + kColDP, q_addr, idesc_acc, 1, false);
-        tc_commit(&bars->a_empty[s]);
-        if (it + 1 < n_it) issue_dpt(it + 1);
+        gemm_ts<D>(tDK, tDS, smem_u32(sQ + sq_ * C::kTileBytes), idesc_acc, it == 0);
+        tc_commit(&bars->a_empty[sq_]);
+        tc_commit(&bars->ds_free[0]);
       }
       if (ok) tc_commit(&bars->acc_full);
     }
@@ -584,63 +635,79 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
     const int row_in_tile = quarter * 32 + lane;
     const int key = key0 + row_in_tile;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t tS = tmem_base + lane_base + kColS + cq * 32;
-    const uint32_t tDP = tmem_base + lane_base + kColDP + cq * 32;
+    const uint32_t tA = tmem_base + lane_base + kColS + cq * 32;         // S^T, then dP^T
+    const uint32_t tP = tmem_base + lane_base + kColDP + cq * 16;        // packed P^T
     const float c = p.scale_log2;
     const float2 c2 = make_float2(c, c);
+    // causal: query column q of tile i is masked for this key when key > q + sk - sq, i.e. the columns of
+    // this thread's quarter below  key - (sk - sq) - (i * 128 + cq * 32)  are masked
+    const int cmin0 = p.is_causal ? key - (sk - sq) - (i_min * kBlock + cq * 32) : 0;
+    const float* stats = sStats + cq * 32;
+    int i_rel = 0;  // Q tile within the current head
     bool ok = true;
+    bool st_ready = false;  // probe of st_full for the coming tile
     for (int it = 0; it < n_it; ++it) {
-      const int s = it % C::kStages;
-      const uint32_t ph = (it / C::kStages) & 1;
-      const int i = i_min + it % per_head;
-      // the statistics of this Q tile arrive with the tile itself
-      if (!(ok = mbar_wait_warp(&bars->a_full[s], ph, ctx))) break;
+      const int ss = it & 1;
+      if (!(ok = warp_wait_unless(st_ready, &bars->st_full[ss], (it >> 1) & 1, ctx))) break;
       if (!(ok = mbar_wait_warp(&bars->s_full, it & 1, ctx))) break;
       tc_fence_after_sync();
       uint32_t sr[32];
-      tmem_ld32(tS, sr);
+      tmem_ld32(tA, sr);
+      const bool p_free_ready = it == 0 || warp_probe(&bars->p_free, (it - 1) & 1);
       tmem_wait_ld();
-      const float2* st_lse = reinterpret_cast<const float2*>(sStats + s * 256 + cq * 32);
-      const float2* st_delta = reinterpret_cast<const float2*>(sStats + s * 256 + 128 + cq * 32);
-      // causal: query column q is masked for this key when key > q + sk - sq
-      int cmin = 0;  // columns below cmin are masked
-      if (p.is_causal) cmin = key - (sk - sq) - (i * kBlock + cq * 32);
+      warp_arrive_loaded(&bars->s_loaded, lane);  // region A may now receive dP^T
+      const float4* st_lse = reinterpret_cast<const float4*>(stats + ss * 256);
+      const float4* st_delta = reinterpret_cast<const float4*>(stats + ss * 256 + 128);
+      const int cmin = cmin0 - i_rel * kBlock;  // columns below cmin are masked
+      if (++i_rel == per_head) i_rel = 0;
       float2 pr[16];
+      uint32_t pk[16];
 #pragma unroll
-      for (int c8 = 0; c8 < 2; ++c8) {
-        uint32_t pk[8];
-#pragma unroll
-        for (int i2 = 0; i2 < 8; ++i2) {
-          const int e = c8 * 8 + i2;
-          const float2 x = ffma2(make_float2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1])), c2, st_lse[e]);
-          float2 pv = exp2_pair(x);
-          if (cmin > 0) {
-            if (2 * e < cmin) pv.x = 0.f;
-            if (2 * e + 1 < cmin) pv.y = 0.f;
-          }
-          pr[e] = pv;
-          pk[i2] = pack_half2(pv.x, pv.y);
-        }
-        tmem_st8(tS + c8 * 8, pk);
-        warp_arrive(&bars->p_full[c8], lane);
+      for (int e = 0; e < 8; ++e) {
+        const float4 l = st_lse[e];
+        pr[2 * e] = exp2_pair(ffma2(make_float2(__uint_as_float(sr[4 * e]), __uint_as_float(sr[4 * e + 1])), c2,
+                                    make_float2(l.x, l.y)));
+        pr[2 * e + 1] = exp2_pair(ffma2(make_float2(__uint_as_float(sr[4 * e + 2]), __uint_as_float(sr[4 * e + 3])),
+                                        c2, make_float2(l.z, l.w)));
       }
+      if (cmin > 0) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          if (2 * e < cmin) pr[e].x = 0.f;
+          if (2 * e + 1 < cmin) pr[e].y = 0.f;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 16; ++e) pk[e] = pack_half2(pr[e].x, pr[e].y);
+      // the dV MMAs of the previous tile must have consumed the old P^T before it is overwritten
+      if (!(ok = warp_wait_unless(p_free_ready, &bars->p_free, (it - 1) & 1, ctx))) break;
+      tmem_st16(tP, pk);
+      const bool dp_ready = warp_probe(&bars->dp_full, it & 1);  // dP^T(it) ran under the exponentials
+      warp_arrive(&bars->p_full, lane);
 
-      if (!(ok = mbar_wait_warp(&bars->dp_full, it & 1, ctx))) break;
+      if (!(ok = warp_wait_unless(dp_ready, &bars->dp_full, it & 1, ctx))) break;
       tc_fence_after_sync();
-      tmem_ld32(tDP, sr);
+      tmem_ld32(tA, sr);
+      const bool ds_free_ready = it == 0 || warp_probe(&bars->ds_free[0], (it - 1) & 1);
+      st_ready = it + 1 < n_it && warp_probe(&bars->st_full[ss ^ 1], ((it + 1) >> 1) & 1);
       tmem_wait_ld();
+      warp_arrive_loaded(&bars->dp_loaded, lane);  // region A may now receive the next S^T
 #pragma unroll
-      for (int c8 = 0; c8 < 2; ++c8) {
-        uint32_t pk[8];
-#pragma unroll
-        for (int i2 = 0; i2 < 8; ++i2) {
-          const int e = c8 * 8 + i2;
-          const float2 d = fmul2(pr[e], fadd2(make_float2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1])), st_delta[e]));
-          pk[i2] = pack_half2(d.x, d.y);
-        }
-        tmem_st8(tDP + c8 * 8, pk);
-        warp_arrive(&bars->ds_full[c8], lane);
+      for (int e = 0; e < 8; ++e) {
+        const float4 dl = st_delta[e];
+        const float2 d0 = fmul2(pr[2 * e], fadd2(make_float2(__uint_as_float(sr[4 * e]), __uint_as_float(sr[4 * e + 1])),
+                                                 make_float2(dl.x, dl.y)));
+        const float2 d1 = fmul2(pr[2 * e + 1], fadd2(make_float2(__uint_as_float(sr[4 * e + 2]), __uint_as_float(sr[4 * e + 3])),
+                                                     make_float2(dl.z, dl.w)));
+        pk[2 * e] = pack_half2(d0.x, d0.y);
+        pk[2 * e + 1] = pack_half2(d1.x, d1.y);
       }
+      // the statistics of this tile are in use no longer
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->st_empty[ss]);
+      if (!(ok = warp_wait_unless(ds_free_ready, &bars->ds_free[0], (it - 1) & 1, ctx))) break;
+      tmem_st16(tP + 64, pk);  // packed dS^T
+      warp_arrive(&bars->ds_full, lane);
     }
     // ---- epilogue: column quarters 0,1 store the halves of dV, quarters 2,3 the halves of dK * scale ----
     const int which = cq >> 1;        // 0 = dV, 1 = dK
@@ -698,18 +765,18 @@ int launch_bwd(const BwdKernelParams& kp, const FaBwdParams* p, int stage_mask, 
   int dev = 0;
   FA_CHECK_CUDA(cudaGetDevice(&dev));
   if (!configured[dev & 63]) {
-    FA_CHECK_CUDA(cudaFuncSetAttribute(bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-    FA_CHECK_CUDA(cudaFuncSetAttribute(bwd_dkdv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    FA_CHECK_CUDA(cudaFuncSetAttribute(bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytesDq));
+    FA_CHECK_CUDA(cudaFuncSetAttribute(bwd_dkdv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytesDkdv));
     configured[dev & 63] = true;
   }
   if (stage_mask & 2) {
     dim3 grid_q((p->seqlen_q + kBlock - 1) / kBlock, p->h, p->b);
-    bwd_dq_kernel<D><<<grid_q, kNumThreads, C::kSmemBytes, stream>>>(kp);
+    bwd_dq_kernel<D><<<grid_q, kNumThreads, C::kSmemBytesDq, stream>>>(kp);
     FA_CHECK_CUDA(cudaGetLastError());
   }
   if (stage_mask & 4) {
     dim3 grid_k((p->seqlen_k + kBlock - 1) / kBlock, p->h_k, p->b);
-    bwd_dkdv_kernel<D><<<grid_k, kNumThreads, C::kSmemBytes, stream>>>(kp);
+    bwd_dkdv_kernel<D><<<grid_k, kNumThreads, C::kSmemBytesDkdv, stream>>>(kp);
     FA_CHECK_CUDA(cudaGetLastError());
   }
   return FA_OK;

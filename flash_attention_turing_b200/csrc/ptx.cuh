@@ -18,6 +18,7 @@ enum : int {
   kStatusOk = 0,
   kStatusWaitTimeout = 1,     // bit 0: a bounded wait gave up; later CTAs return at once, outputs are invalid
   kStatusCapacityClamped = 2, // bit 1: a cache length exceeded the cache capacity and was clamped on the device
+  kStatusSmemLayout = 4,      // bit 2: dynamic shared memory did not start on a 1024-byte boundary; the kernel did no work
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -73,6 +74,21 @@ __device__ __forceinline__ uint32_t mbar_test(uint64_t* bar, uint32_t parity) {
       "{\n\t"
       ".reg .pred P;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok;
+}
+
+// Non-blocking form (try_wait may suspend the thread for a while when the phase is incomplete).
+__device__ __forceinline__ uint32_t mbar_test_nonblocking(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, P;\n\t"
       "}\n"
       : "=r"(ok)

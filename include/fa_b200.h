@@ -49,7 +49,10 @@ int fa_abi_version(void);
  * (value 1) = a wait timed out and the outputs of that launch are invalid; bit 1 (value 2) = a cache
  * length (cache_seqlens + seqlen_new, or seqused_k) exceeded the cache capacity and was clamped on the
  * device, so that a host that skips the reference's synchronising capacity check
- * (csrc/flash_attn/flash_api.cpp:627) still never reads or writes out of bounds; negative = FA_ERR_*.  With
+ * (csrc/flash_attn/flash_api.cpp:627) still never reads or writes out of bounds; bit 2 (value 4) = the
+ * dK/dV kernel found its dynamic shared memory not aligned to 1024 bytes (its head-size-128 layout has
+ * no room for an alignment pad) and did no work, so dK and dV of that launch are invalid; negative =
+ * FA_ERR_*.  With
  * reset != 0 the word is cleared afterwards.  No counterpart in the reference, whose launches are
  * not error-checked at all (src/flash_fwd_launch_template.h:73-89). */
 int fa_device_status(int reset);
