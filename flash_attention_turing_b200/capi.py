@@ -25,6 +25,7 @@ EXPORTED_SYMBOLS = (
     "fa_kvcache_noalloc",
     "fa_combine",
     "fa_combine_gather",
+    "fa_sum_gather",
 )
 
 _i64, _i32, _f32, _vp, _sz = C.c_int64, C.c_int32, C.c_float, C.c_void_p, C.c_size_t
@@ -84,6 +85,11 @@ class FaCombineGatherParams(C.Structure):
                 ("reserved0", _i32)]
 
 
+class FaSumGatherParams(C.Structure):
+    _fields_ = [("part", _vp * 16), ("out", _vp), ("num_parts", _i32), ("b", _i32), ("h", _i32), ("seqlen_q", _i32),
+                ("d", _i32), ("row_begin", _i32), ("rows", _i32), ("reserved0", _i32)]
+
+
 class FaError(RuntimeError):
     def __init__(self, code: int, message: str):
         super().__init__(f"libfa_b200 error {code}: {message}")
@@ -112,6 +118,8 @@ def lib() -> C.CDLL:
             fn.argtypes = [C.POINTER(struct), _vp]
         l.fa_combine_gather.restype = C.c_int
         l.fa_combine_gather.argtypes = [C.POINTER(FaCombineGatherParams), _vp]
+        l.fa_sum_gather.restype = C.c_int
+        l.fa_sum_gather.argtypes = [C.POINTER(FaSumGatherParams), _vp]
         l.fa_bwd_stages.restype = C.c_int
         l.fa_bwd_stages.argtypes = [C.POINTER(FaBwdParams), C.c_int, _vp]
         l.fa_bwd_workspace_bytes.restype = _sz

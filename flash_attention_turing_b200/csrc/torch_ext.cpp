@@ -442,6 +442,31 @@ std::vector<at::Tensor> combine_gather(std::vector<at::Tensor> o_parts, std::vec
   return {out, lse};
 }
 
+// ---- sum of per-rank partial dQ read in place (parts[r] may be peer-mapped memory of another GPU) ----
+at::Tensor sum_gather(std::vector<at::Tensor> parts, int64_t row_begin, int64_t rows) {
+  TORCH_CHECK(!parts.empty() && parts.size() <= FA_MAX_GATHER_PARTS, "between 1 and ", FA_MAX_GATHER_PARTS, " parts");
+  const at::Tensor& p0 = parts[0];
+  TORCH_CHECK(p0.dim() == 4, "partial dQ must be (b, seqlen_q, h, d)");
+  const int64_t b = p0.size(0), s = p0.size(1), h = p0.size(2), d = p0.size(3);
+  check_supported_head_dim(d);
+  FaSumGatherParams p = {};
+  for (size_t i = 0; i < parts.size(); ++i) {
+    TORCH_CHECK(parts[i].is_cuda() && parts[i].scalar_type() == at::kHalf && parts[i].is_contiguous() &&
+                    parts[i].sizes() == p0.sizes(),
+                "partial dQ tensors must be contiguous float16 CUDA tensors of one shape");
+    p.part[i] = parts[i].data_ptr();
+  }
+  TORCH_CHECK(row_begin >= 0 && rows >= 0 && row_begin + rows <= s, "row range out of bounds");
+  auto opts = at::TensorOptions().device(at::kCUDA, at::cuda::current_device());
+  at::Tensor out = torch::empty({b, rows, h, d}, opts.dtype(torch::kFloat16));
+  p.out = out.data_ptr();
+  p.num_parts = static_cast<int32_t>(parts.size());
+  p.b = b; p.h = h; p.seqlen_q = s; p.d = d;
+  p.row_begin = row_begin; p.rows = rows;
+  if (b > 0 && rows > 0) check_rc(fa_sum_gather(&p, current_stream()), "fa_sum_gather");
+  return out;
+}
+
 int64_t device_status(bool reset) { return fa_device_status(reset ? 1 : 0); }
 
 }  // namespace
@@ -454,5 +479,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fwd_kvcache", &mha_fwd_kvcache, "KV-cache forward pass");
   m.def("combine", &combine, "Merge split partials (O fp32, LSE) with log-sum-exp weights");
   m.def("combine_gather", &combine_gather, "Merge per-rank partial (O fp16, LSE) read in place, peer memory allowed");
+  m.def("sum_gather", &sum_gather, "Sum per-rank partial dQ (fp16) read in place, peer memory allowed");
   m.def("device_status", &device_status, "Synchronise and read the device status word");
 }

@@ -1,5 +1,7 @@
-"""Sequence-sharded forward: each rank holds one contiguous shard of K/V, attends ALL queries against
-it, and the partial (O, LSE) of the ranks are merged with the split-KV log-sum-exp combine.
+"""Sequence-sharded forward and backward: each rank holds one contiguous shard of K/V, attends ALL
+queries against it, and the partial (O, LSE) of the ranks are merged with the split-KV log-sum-exp
+combine.  In the backward every rank obtains dK/dV of its shard completely and its keys' share of dQ;
+the shares are summed across the ranks.
 
 This is the one place of the attention path that has a real exchange step.  The reference has no
 multi-GPU code; the merge is its split-KV combine (``kvcache_combine_kernel``,
@@ -10,7 +12,13 @@ rank.  Plumbing is ``torch.distributed`` (NCCL over NVLink on GPUs; gloo in the 
     all_to_all_single: query-row slice j of every rank's partial -> rank j       (one collective)
     rank j:  out[slice j] = combine(partials of slice j)                         (fa_combine)
 
-No peer memory is read by any kernel: the collective lands the partials in local memory first.
+    backward, rank r:  dq_share_r, dk[shard r], dv[shard r] = backward(q, k[shard r], v[shard r],
+                                                   merged out, merged lse, dout)   (local kernels)
+    all_to_all_single: query-row slice j of every rank's dq share -> rank j        (one collective)
+    rank j:  dq[slice j] = sum of the shares of slice j                            (fa_sum_gather)
+
+In these paths no kernel reads peer memory: the collective lands the partials in local memory first.
+The ``*_p2p`` variants replace the collective by ONE kernel that reads the peers' buffers in place.
 
 ``partial_attention`` and ``merge_partials`` take the kernels as injectable callables so that the
 exchange logic can be exercised by CPU ranks in the tests (with the oracle as the kernel stand-in);
@@ -24,6 +32,9 @@ import torch
 import torch.distributed as dist
 
 FwdFn = Callable[[torch.Tensor, torch.Tensor, torch.Tensor, float, bool], Tuple[torch.Tensor, torch.Tensor]]
+# (q, k, v, out, lse, dout, scale, causal) -> (dq, dk, dv), from SAVED out / lse as the extension's bwd does
+BwdFn = Callable[..., Tuple[torch.Tensor, torch.Tensor, torch.Tensor]]
+SumFn = Callable[[torch.Tensor], torch.Tensor]  # (world, b, sl, h, d) shares -> (b, sl, h, d) sum
 CombineFn = Callable[[torch.Tensor, torch.Tensor, int, int, int], Tuple[torch.Tensor, torch.Tensor]]
 
 
@@ -37,6 +48,18 @@ def _default_combine(o_accum, lse_accum, b, sq, h):
     from . import _ext
 
     return _ext.load().combine(o_accum, lse_accum, b, sq, h)
+
+
+def _default_bwd(q, k, v, out, lse, dout, scale, causal):
+    from . import _ext
+
+    return _ext.load().bwd(q, k, v, out, lse, dout, scale, causal)
+
+
+def _default_sum(shares):
+    from . import _ext
+
+    return _ext.load().sum_gather(list(shares.unbind(0)), 0, shares.shape[2])
 
 
 def partial_attention(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, key_offset: int,
@@ -173,3 +196,109 @@ def sequence_parallel_forward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_shar
     out, lse = ext.combine_gather(o_parts, l_parts, rank * sl, sl)
     hdl_o.barrier(channel=1)  # nobody overwrites a partial that a peer is still reading
     return out, lse
+
+
+# ------------------------------------------------------------------------------------------------
+# Backward
+# ------------------------------------------------------------------------------------------------
+def partial_backward(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, out: torch.Tensor,
+                     lse: torch.Tensor, dout: torch.Tensor, key_offset: int, softmax_scale: float, causal: bool,
+                     bwd: Optional[BwdFn] = None, dq_share: Optional[torch.Tensor] = None
+                     ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Backward of all queries against one K/V shard that starts at global key index ``key_offset``.
+
+    ``out`` (b, s, h, d) and ``lse`` (b, h, s) are the MERGED results of the forward for all query rows,
+    ``dout`` the gradient of ``out``.  Because the kernels recompute P = exp(scale S - lse) from the saved
+    lse and D = rowsum(dO o out) from the saved out, running them on the shard's keys alone gives the exact
+    dK, dV of the shard and the shard's share of dQ.  Returns (dq_share (b, s, h, d), dk_shard, dv_shard) in
+    the input dtype; dq_share is zero for rows that see no key of the shard.  Causal: the same two launches
+    as in ``partial_attention`` (square causal problem on the shard's diagonal, dense rectangle below it),
+    with dK / dV of the two added in fp32."""
+    bwd = bwd or _default_bwd
+    b, s, h, d = q.shape
+    s_shard = k_shard.shape[1]
+    if dq_share is None:
+        dq_share = torch.empty_like(q)
+    if s_shard == 0:
+        dq_share.zero_()
+        return dq_share, torch.zeros_like(k_shard), torch.zeros_like(v_shard)
+    if not causal:
+        dq, dk, dv = bwd(q, k_shard, v_shard, out, lse.contiguous(), dout, softmax_scale, False)
+        dq_share.copy_(dq)
+        return dq_share, dk, dv
+    lo = min(key_offset, s)
+    mid = min(key_offset + s_shard, s)
+    dq_share[:, :lo].zero_()
+    dk = torch.zeros(k_shard.shape, dtype=torch.float32, device=k_shard.device)
+    dv = torch.zeros(v_shard.shape, dtype=torch.float32, device=v_shard.device)
+    if mid > lo:  # diagonal block: square causal problem
+        n = mid - lo
+        dq, dk_a, dv_a = bwd(q[:, lo:mid], k_shard[:, :n], v_shard[:, :n], out[:, lo:mid],
+                             lse[:, :, lo:mid].contiguous(), dout[:, lo:mid], softmax_scale, True)
+        dq_share[:, lo:mid] = dq
+        dk[:, :n] += dk_a.float()
+        dv[:, :n] += dv_a.float()
+    if s > mid:  # rows below the diagonal block see the whole shard
+        dq, dk_b, dv_b = bwd(q[:, mid:], k_shard, v_shard, out[:, mid:], lse[:, :, mid:].contiguous(),
+                             dout[:, mid:], softmax_scale, False)
+        dq_share[:, mid:] = dq
+        dk += dk_b.float()
+        dv += dv_b.float()
+    return dq_share, dk.to(k_shard.dtype), dv.to(v_shard.dtype)
+
+
+def reduce_dq_shares(dq_share: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
+                     sum_parts: Optional[SumFn] = None) -> torch.Tensor:
+    """Exchange and sum.  dq_share (b, s, h, d) is this rank's share for ALL query rows; returns this rank's
+    query-row slice of the sum, (b, s / world, h, d).  The shares travel in their own dtype (half the bytes
+    of an fp32 reduce-scatter) and are added in fp32 on arrival."""
+    sum_parts = sum_parts or _default_sum
+    world = dist.get_world_size(group)
+    b, s, h, d = dq_share.shape
+    if s % world != 0:
+        raise ValueError("seqlen_q must be divisible by the number of ranks")
+    sl = s // world
+    send = dq_share.view(b, world, sl, h, d).transpose(0, 1).contiguous()  # (world, b, sl, h, d)
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    return sum_parts(recv)
+
+
+def sequence_parallel_backward(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, out: torch.Tensor,
+                               lse: torch.Tensor, dout: torch.Tensor, softmax_scale: Optional[float] = None,
+                               causal: bool = False, group: Optional[dist.ProcessGroup] = None,
+                               bwd: Optional[BwdFn] = None, sum_parts: Optional[SumFn] = None):
+    """Backward of ``sequence_parallel_forward``.  q, dout and the merged out (b, s, h, d) / lse (b, h, s) are
+    replicated (all query rows on every rank, e.g. from ``gather_output=True``); K/V are sharded as in the
+    forward.  Returns (dq for this rank's query-row slice (b, s / world, h, d), dk_shard, dv_shard)."""
+    rank = dist.get_rank(group)
+    scale = q.shape[-1] ** -0.5 if softmax_scale is None else softmax_scale
+    dq_share, dk, dv = partial_backward(q, k_shard, v_shard, out, lse, dout, rank * k_shard.shape[1], scale, causal,
+                                        bwd)
+    return reduce_dq_shares(dq_share, group, sum_parts), dk, dv
+
+
+def sequence_parallel_backward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, out: torch.Tensor,
+                                   lse: torch.Tensor, dout: torch.Tensor, softmax_scale: Optional[float] = None,
+                                   causal: bool = False, group: Optional[dist.ProcessGroup] = None):
+    """Same result as ``sequence_parallel_backward`` without the all-to-all: the dQ shares are written into
+    symmetric memory, a device-side barrier orders the ranks, and ONE kernel (``fa_sum_gather``) reads the
+    query-row slice of every rank's share straight from that rank's HBM over NVLink (plain loads, no
+    multicast) and adds them."""
+    from . import _ext
+
+    ext = _ext.load()
+    rank = dist.get_rank(group)
+    world = dist.get_world_size(group)
+    b, s, h, d = q.shape
+    if s % world != 0:
+        raise ValueError("seqlen_q must be divisible by the number of ranks")
+    scale = d ** -0.5 if softmax_scale is None else softmax_scale
+    buf, _, hdl, _ = _p2p_buffers(q.shape, (b, h, s), q.dtype, q.device, group)
+    _, dk, dv = partial_backward(q, k_shard, v_shard, out, lse, dout, rank * k_shard.shape[1], scale, causal, None, buf)
+    hdl.barrier(channel=0)  # every rank's share is complete and visible
+    parts = [hdl.get_buffer(r, q.shape, q.dtype) for r in range(world)]
+    sl = s // world
+    dq = ext.sum_gather(parts, rank * sl, sl)
+    hdl.barrier(channel=1)  # nobody overwrites a share that a peer is still reading
+    return dq, dk, dv

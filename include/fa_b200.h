@@ -260,6 +260,26 @@ typedef struct FaCombineGatherParams {
 
 int fa_combine_gather(const FaCombineGatherParams* p, fa_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------- */
+/* Sum of per-rank partial gradients of a sequence-sharded backward, read where they are: with   */
+/* K/V sharded by sequence every rank computes dK/dV of its own shard completely, but only its   */
+/* keys' share of dQ; the shares add up.  part[r] is rank r's fp16 dQ share for ALL query rows,   */
+/* (b, seqlen_q, h, d) contiguous, and may point into another GPU's memory (peer-mapped, plain   */
+/* loads over NVLink).  This call adds rows [row_begin, row_begin + rows) of every part in fp32   */
+/* and writes out (b, rows, h, d) fp16 -- exchange and reduction in one kernel.  No counterpart  */
+/* in the reference (it has no multi-GPU code; its only cross-CTA gradient sum is the GQA        */
+/* torch::sum_out of flash_api.cpp:338-348).                                                     */
+/* ------------------------------------------------------------------------------------------- */
+typedef struct FaSumGatherParams {
+  const void* part[FA_MAX_GATHER_PARTS];
+  void* out;
+  int32_t num_parts, b, h, seqlen_q, d;
+  int32_t row_begin, rows;
+  int32_t reserved0;
+} FaSumGatherParams;
+
+int fa_sum_gather(const FaSumGatherParams* p, fa_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

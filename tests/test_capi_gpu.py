@@ -95,6 +95,30 @@ def test_fa_combine_raw():
     assert out.float().cpu().permute(0, 2, 1, 3).reshape(rows, d)[7].abs().max().item() == 0
 
 
+def test_fa_sum_gather_raw():
+    from flash_attention_turing_b200 import capi
+
+    lib = capi.lib()
+    for n, b, s, h, d, row_begin, rows in ((3, 2, 10, 3, 64, 4, 5), (16, 1, 7, 2, 128, 0, 7), (1, 2, 4, 1, 64, 3, 1)):
+        gen = torch.Generator().manual_seed(n)
+        parts = [torch.randn(b, s, h, d, generator=gen).half() for _ in range(n)]
+        want = sum(x[:, row_begin:row_begin + rows].float() for x in parts)
+        dev_parts = [x.to(DEV) for x in parts]
+        out = torch.empty(b, rows, h, d, dtype=torch.half, device=DEV)
+        p = capi.FaSumGatherParams()
+        for i, x in enumerate(dev_parts):
+            p.part[i] = x.data_ptr()
+        p.out = out.data_ptr()
+        p.num_parts, p.b, p.h, p.seqlen_q, p.d, p.row_begin, p.rows = n, b, h, s, d, row_begin, rows
+        capi.check(lib.fa_sum_gather(ctypes.byref(p), _stream()))
+        torch.cuda.synchronize()
+        # fp32 sum rounded once to fp16
+        assert torch.equal(out.cpu(), want.half())
+    p.num_parts = 17
+    assert lib.fa_sum_gather(ctypes.byref(p), _stream()) != 0
+    assert b"num_parts" in lib.fa_last_error()
+
+
 def test_fa_kvcache_raw_paged():
     from flash_attention_turing_b200 import capi
 

@@ -1,4 +1,4 @@
-"""World-size-2 (and 4) gloo tests of the sequence-sharded forward's exchange logic on CPU ranks.
+"""World-size-2 (and 4) gloo tests of the sequence-sharded forward's and backward's exchange logic on CPU ranks.
 
 The kernels are injected: the CPU oracle stands in for the forward kernel and for the combine kernel,
 so what is tested here is the sharding arithmetic (causal offsets per shard), the all-to-all layout and
@@ -81,3 +81,78 @@ def test_partial_attention_rows_before_the_shard_are_neutral():
     assert torch.isinf(lse[:, :, :8]).all() and (lse[:, :, :8] < 0).all()
     assert out[:, :8].abs().max().item() == 0
     assert torch.isfinite(lse[:, :, 8:]).all()
+
+
+# ------------------------------------------------------------------------------------------------
+# backward: shard-local dK/dV, dQ shares summed across ranks
+# ------------------------------------------------------------------------------------------------
+def _oracle_bwd(q, k, v, out, lse, dout, scale, causal):
+    return orc.attention_backward_given_lse(q, k, v, out, lse, dout, scale, causal)
+
+
+def _oracle_sum(shares):
+    return shares.float().sum(0)
+
+
+def _bwd_worker(rank, world, port, causal, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from flash_attention_turing_b200 import seq_parallel as sp
+
+        torch.manual_seed(9)  # same data on every rank
+        b, s, h, hk, d = 2, 64, 4, 2, 64
+        q, dout = torch.randn(b, s, h, d), torch.randn(b, s, h, d)
+        k, v = torch.randn(b, s, hk, d), torch.randn(b, s, hk, d)
+        shard = s // world
+        ks, vs = k[:, rank * shard:(rank + 1) * shard], v[:, rank * shard:(rank + 1) * shard]
+        out, lse = sp.sequence_parallel_forward(q, ks, vs, None, causal, gather_output=True,
+                                                fwd=_oracle_fwd, combine=_oracle_combine)
+        dq, dk, dv = sp.sequence_parallel_backward(q, ks, vs, out, lse, dout, None, causal,
+                                                   bwd=_oracle_bwd, sum_parts=_oracle_sum)
+        rq, rk, rv = orc.attention_backward(q, k, v, dout, None, causal)
+        sl = s // world
+        results[rank] = ((dq - rq[:, rank * sl:(rank + 1) * sl]).abs().max().item(),
+                         (dk - rk[:, rank * shard:(rank + 1) * shard]).abs().max().item(),
+                         (dv - rv[:, rank * shard:(rank + 1) * shard]).abs().max().item())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("causal", [False, True])
+def test_sequence_parallel_backward_matches_single_process(world, causal):
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_bwd_worker, args=(world, _free_port(), causal, results), nprocs=world, join=True)
+    assert len(results) == world
+    for rank in range(world):
+        assert max(results[rank]) < 2e-5, (rank, results[rank])
+
+
+def test_backward_from_saved_statistics_equals_recomputed_backward():
+    torch.manual_seed(3)
+    q, dout = torch.randn(1, 24, 4, 64), torch.randn(1, 24, 4, 64)
+    k, v = torch.randn(1, 40, 2, 64), torch.randn(1, 40, 2, 64)
+    for causal in (False, True):
+        out, lse = orc.attention_forward(q, k, v, None, causal)
+        got = orc.attention_backward_given_lse(q, k, v, out, lse, dout, None, causal)
+        want = orc.attention_backward(q, k, v, dout, None, causal)
+        for g, w in zip(got, want):
+            assert (g - w).abs().max().item() < 1e-5
+
+
+def test_partial_backward_rows_before_the_shard_get_no_gradient():
+    from flash_attention_turing_b200 import seq_parallel as sp
+
+    torch.manual_seed(1)
+    q, dout = torch.randn(1, 16, 2, 64), torch.randn(1, 16, 2, 64)
+    k, v = torch.randn(1, 16, 2, 64), torch.randn(1, 16, 2, 64)
+    out, lse = orc.attention_forward(q, k, v, 0.125, True)
+    dq, dk, dv = sp.partial_backward(q, k[:, 8:12], v[:, 8:12], out, lse, dout, key_offset=8, softmax_scale=0.125,
+                                     causal=True, bwd=_oracle_bwd)
+    assert dq[:, :8].abs().max().item() == 0
+    assert dq[:, 8:].abs().max().item() > 0
+    rq, rk, rv = orc.attention_backward(q, k, v, dout, 0.125, True)
+    assert (dk - rk[:, 8:12]).abs().max().item() < 1e-5 and (dv - rv[:, 8:12]).abs().max().item() < 1e-5

@@ -1,5 +1,5 @@
-"""Sequence-sharded forward on two GPUs over NCCL, checked against the single-GPU kernel and the CPU
-oracle.  Skipped on a box with fewer than two GPUs."""
+"""Sequence-sharded forward and backward on two GPUs over NCCL, checked against the single-GPU kernels and
+the CPU oracle.  Skipped on a box with fewer than two GPUs."""
 import os
 import socket
 
@@ -76,3 +76,64 @@ def test_two_gpu_sequence_parallel_forward(causal, d):
         assert err_o <= 3e-3, (rank, err_o)       # fp16 partials merged: two fp16 roundings
         assert err_l <= 1e-3, (rank, err_l)
         assert err_one <= 3e-3, (rank, err_one)
+
+
+def _bwd_worker(rank, world, port, causal, d, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from flash_attention_turing_b200 import _ext, seq_parallel as sp
+        from oracle import attention_oracle as orc
+
+        ext = _ext.load()
+        gen = torch.Generator().manual_seed(17)  # same data on every rank
+        b, s, h, hk = 1, 1024, 4, 2
+        q = torch.randn(b, s, h, d, generator=gen).half()
+        k = torch.randn(b, s, hk, d, generator=gen).half()
+        v = torch.randn(b, s, hk, d, generator=gen).half()
+        dout = torch.randn(b, s, h, d, generator=gen).half()
+        shard = s // world
+        sl = s // world
+        qd, dod = q.to(dev), dout.to(dev)
+        ks = k[:, rank * shard:(rank + 1) * shard].contiguous().to(dev)
+        vs = v[:, rank * shard:(rank + 1) * shard].contiguous().to(dev)
+        out, lse = sp.sequence_parallel_forward(qd, ks, vs, None, causal, gather_output=True)
+        dq, dk, dv = sp.sequence_parallel_backward(qd, ks, vs, out, lse, dod, None, causal)
+        torch.cuda.synchronize()
+        p2p_err = -1.0
+        try:
+            dq_p, dk_p, dv_p = sp.sequence_parallel_backward_p2p(qd, ks, vs, out, lse, dod, None, causal)
+            torch.cuda.synchronize()
+            p2p_err = max((dq_p.float() - dq.float()).abs().max().item(), (dk_p.float() - dk.float()).abs().max().item(),
+                          (dv_p.float() - dv.float()).abs().max().item())
+        except (ImportError, RuntimeError) as exc:  # symmetric memory not usable on this box
+            print("p2p path unavailable:", exc)
+        rq, rk, rv = orc.attention_backward(q, k, v, dout, None, causal)
+        errs = ((dq.float().cpu() - rq[:, rank * sl:(rank + 1) * sl]).abs().max().item(),
+                (dk.float().cpu() - rk[:, rank * shard:(rank + 1) * shard]).abs().max().item(),
+                (dv.float().cpu() - rv[:, rank * shard:(rank + 1) * shard]).abs().max().item())
+        scale = max(rq.abs().max().item(), rk.abs().max().item(), rv.abs().max().item())
+        results[rank] = (errs, scale, int(ext.device_status(True)), p2p_err)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("d", [64, 128])
+def test_two_gpu_sequence_parallel_backward(causal, d):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_bwd_worker, args=(world, _free_port(), causal, d, results), nprocs=world, join=True)
+    for rank in range(world):
+        errs, scale, status, p2p_err = results[rank]
+        assert status == 0
+        assert p2p_err <= 1e-6, (rank, p2p_err)  # same kernels, same order of additions; -1 when unavailable
+        # fp16 gradients, the dQ shares rounded to fp16 before they are summed
+        assert max(errs) <= 4e-3 + 2.0 ** -9 * scale, (rank, errs, scale)
