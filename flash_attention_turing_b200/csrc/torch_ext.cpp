@@ -134,8 +134,27 @@ std::vector<at::Tensor> mha_varlen_fwd(at::Tensor q, at::Tensor k, at::Tensor v,
 }
 
 // ---- dense backward (mha_bwd, flash_api.cpp:258-351) ----
+// Gradient destination given by the caller (e.g. a view into a packed dqkv tensor) or allocated here.
+at::Tensor grad_destination(const c10::optional<at::Tensor>& given, const at::Tensor& like, const char* name,
+                            bool zero_init) {
+  if (!given.has_value() || !given->defined())
+    return zero_init ? torch::zeros_like(like, like.options(), at::MemoryFormat::Contiguous)
+                     : torch::empty_like(like, like.options(), at::MemoryFormat::Contiguous);
+  const at::Tensor& g = *given;
+  TORCH_CHECK(g.is_cuda() && g.scalar_type() == torch::kFloat16 && g.device() == like.device(), name,
+              " must be a float16 CUDA tensor on the device of its input");
+  TORCH_CHECK(g.sizes() == like.sizes(), name, " must have the shape of its input");
+  TORCH_CHECK(g.stride(-1) == 1, name, " must have a contiguous last dimension");
+  if (zero_init) g.zero_();
+  return g;
+}
+
+// dq_, dk_, dv_ (optional, after the reference's eight arguments): write the gradients there instead of
+// into new tensors; strided views are fine (16-byte aligned, strides multiples of 8 elements).
 std::vector<at::Tensor> mha_bwd(at::Tensor q, at::Tensor k, at::Tensor v, at::Tensor out, at::Tensor l,
-                                at::Tensor dout, const double softmax_scale, bool is_causal) {
+                                at::Tensor dout, const double softmax_scale, bool is_causal,
+                                c10::optional<at::Tensor> dq_, c10::optional<at::Tensor> dk_,
+                                c10::optional<at::Tensor> dv_) {
   TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "q, k, v must be rank-4 tensors");
   TORCH_CHECK(out.dim() == 4 && dout.dim() == 4, "out and dout must be rank-4 tensors");
   check_half_cuda(q, "q"); check_half_cuda(k, "k"); check_half_cuda(v, "v");
@@ -155,9 +174,9 @@ std::vector<at::Tensor> mha_bwd(at::Tensor q, at::Tensor k, at::Tensor v, at::Te
               "l must have shape [batch_size, nheads_q, seqlen_q]");
   c10::cuda::CUDAGuard guard(q.device());
 
-  at::Tensor dq = torch::empty_like(q, q.options(), at::MemoryFormat::Contiguous);
-  at::Tensor dk = torch::empty_like(k, k.options(), at::MemoryFormat::Contiguous);
-  at::Tensor dv = torch::empty_like(v, v.options(), at::MemoryFormat::Contiguous);
+  at::Tensor dq = grad_destination(dq_, q, "dq", false);
+  at::Tensor dk = grad_destination(dk_, k, "dk", false);
+  at::Tensor dv = grad_destination(dv_, v, "dv", false);
   if (batch_size == 0 || seqlen_q == 0 || seqlen_k == 0) {
     dq.zero_(); dk.zero_(); dv.zero_();
     return {dq, dk, dv};
@@ -192,7 +211,9 @@ std::vector<at::Tensor> mha_bwd(at::Tensor q, at::Tensor k, at::Tensor v, at::Te
 std::vector<at::Tensor> mha_varlen_bwd(at::Tensor q, at::Tensor k, at::Tensor v, at::Tensor out, at::Tensor l,
                                        at::Tensor dout, at::Tensor cu_seqlens_q, at::Tensor cu_seqlens_k,
                                        const int64_t max_seqlen_q, const int64_t max_seqlen_k,
-                                       const double softmax_scale, bool is_causal) {
+                                       const double softmax_scale, bool is_causal,
+                                       c10::optional<at::Tensor> dq_, c10::optional<at::Tensor> dk_,
+                                       c10::optional<at::Tensor> dv_) {
   check_varlen_qkv(q, k, v);
   check_cu_seqlens(cu_seqlens_q, cu_seqlens_k);
   check_half_cuda(out, "out");
@@ -209,9 +230,9 @@ std::vector<at::Tensor> mha_varlen_bwd(at::Tensor q, at::Tensor k, at::Tensor v,
   c10::cuda::CUDAGuard guard(q.device());
 
   // rows outside every sequence stay zero, as in the reference (torch::zeros_like, :462-464)
-  at::Tensor dq = torch::zeros_like(q, q.options(), at::MemoryFormat::Contiguous);
-  at::Tensor dk = torch::zeros_like(k, k.options(), at::MemoryFormat::Contiguous);
-  at::Tensor dv = torch::zeros_like(v, v.options(), at::MemoryFormat::Contiguous);
+  at::Tensor dq = grad_destination(dq_, q, "dq", true);
+  at::Tensor dk = grad_destination(dk_, k, "dk", true);
+  at::Tensor dv = grad_destination(dv_, v, "dv", true);
   if (q.size(0) == 0 || k.size(0) == 0 || max_seqlen_q <= 0 || max_seqlen_k <= 0) return {dq, dk, dv};
 
   FaBwdParams p = {};
@@ -473,9 +494,14 @@ int64_t device_status(bool reset) { return fa_device_status(reset ? 1 : 0); }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fwd", &mha_fwd, "Forward pass");
-  m.def("bwd", &mha_bwd, "Backward pass");
+  m.def("bwd", &mha_bwd, "Backward pass", py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("l"),
+        py::arg("dout"), py::arg("softmax_scale"), py::arg("is_causal"), py::arg("dq") = py::none(),
+        py::arg("dk") = py::none(), py::arg("dv") = py::none());
   m.def("varlen_fwd", &mha_varlen_fwd, "Varlen forward pass");
-  m.def("varlen_bwd", &mha_varlen_bwd, "Varlen backward pass");
+  m.def("varlen_bwd", &mha_varlen_bwd, "Varlen backward pass", py::arg("q"), py::arg("k"), py::arg("v"),
+        py::arg("out"), py::arg("l"), py::arg("dout"), py::arg("cu_seqlens_q"), py::arg("cu_seqlens_k"),
+        py::arg("max_seqlen_q"), py::arg("max_seqlen_k"), py::arg("softmax_scale"), py::arg("is_causal"),
+        py::arg("dq") = py::none(), py::arg("dk") = py::none(), py::arg("dv") = py::none());
   m.def("fwd_kvcache", &mha_fwd_kvcache, "KV-cache forward pass");
   m.def("combine", &combine, "Merge split partials (O fp32, LSE) with log-sum-exp weights");
   m.def("combine_gather", &combine_gather, "Merge per-rank partial (O fp16, LSE) read in place, peer memory allowed");

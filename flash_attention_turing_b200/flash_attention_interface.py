@@ -55,9 +55,11 @@ def _flash_attn_forward(q, k, v, softmax_scale: float, causal: bool):
     return out, lse
 
 
-def _flash_attn_backward(dout, q, k, v, out, lse, softmax_scale: float, causal: bool):
+def _flash_attn_backward(dout, q, k, v, out, lse, softmax_scale: float, causal: bool, grads=()):
+    """``grads``: optional (dq, dk, dv) destinations, e.g. views into one packed gradient tensor; the kernels
+    write through their strides, so the packed variants need no concatenation afterwards."""
     dout, q, k, v, out, lse = (maybe_contiguous(t) for t in (dout, q, k, v, out, lse))
-    dq, dk, dv = _gpu().bwd(q, k, v, out, lse, dout, softmax_scale, causal)
+    dq, dk, dv = _gpu().bwd(q, k, v, out, lse, dout, softmax_scale, causal, *grads)
     return dq, dk, dv
 
 
@@ -70,10 +72,10 @@ def _flash_attn_varlen_forward(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q
 
 
 def _flash_attn_varlen_backward(dout, q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int,
-                                max_seqlen_k: int, softmax_scale: float, causal: bool):
+                                max_seqlen_k: int, softmax_scale: float, causal: bool, grads=()):
     dout, q, k, v, out, lse = (maybe_contiguous(t) for t in (dout, q, k, v, out, lse))
     dq, dk, dv = _gpu().varlen_bwd(q, k, v, out, lse, dout, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
-                                   max_seqlen_k, softmax_scale, causal)
+                                   max_seqlen_k, softmax_scale, causal, *grads)
     return dq, dk, dv
 
 
@@ -99,9 +101,18 @@ def _save_dense(ctx, needs_grad, q, k, v, out, lse, softmax_scale, causal):
         ctx.causal = causal
 
 
-def _dense_backward(ctx, dout):
+def _dense_backward(ctx, dout, grads=()):
     q, k, v, out, lse = ctx.saved_tensors
-    return _flash_attn_backward(dout, q, k, v, out, lse, ctx.softmax_scale, ctx.causal)
+    return _flash_attn_backward(dout, q, k, v, out, lse, ctx.softmax_scale, ctx.causal, grads)
+
+
+def _packed_like(parts, dim):
+    """One packed gradient tensor for ``parts`` (same-shape q/k/v views) stacked along ``dim``, and its
+    unbound views: the layout the reference builds by concatenation (:226-231, :262-264)."""
+    shape = list(parts[0].shape)
+    shape.insert(dim, len(parts))
+    packed = torch.empty(shape, dtype=parts[0].dtype, device=parts[0].device)
+    return packed, packed.unbind(dim=dim)
 
 
 class FlashAttnFunc(torch.autograd.Function):
@@ -130,8 +141,10 @@ class FlashAttnQKVPackedFunc(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
-        dq, dk, dv = _dense_backward(ctx, dout)
-        return torch.stack((dq, dk, dv), dim=2), None, None, None
+        q, k, v = ctx.saved_tensors[:3]
+        dqkv, views = _packed_like((q, k, v), 2)
+        _dense_backward(ctx, dout, views)
+        return dqkv, None, None, None
 
 
 class FlashAttnKVPackedFunc(torch.autograd.Function):
@@ -146,8 +159,10 @@ class FlashAttnKVPackedFunc(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
-        dq, dk, dv = _dense_backward(ctx, dout)
-        return dq, torch.stack((dk, dv), dim=2), None, None, None
+        q, k, v = ctx.saved_tensors[:3]
+        dkv, (dk, dv) = _packed_like((k, v), 2)
+        dq, _, _ = _dense_backward(ctx, dout, (torch.empty_like(q), dk, dv))
+        return dq, dkv, None, None, None
 
 
 def _save_varlen(ctx, needs_grad, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, softmax_scale, causal):
@@ -159,10 +174,10 @@ def _save_varlen(ctx, needs_grad, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, s
         ctx.causal = causal
 
 
-def _varlen_backward(ctx, dout):
+def _varlen_backward(ctx, dout, grads=()):
     q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
     return _flash_attn_varlen_backward(dout, q, k, v, out, lse, cu_q, cu_k, ctx.max_seqlen_q,
-                                       ctx.max_seqlen_k, ctx.softmax_scale, ctx.causal)
+                                       ctx.max_seqlen_k, ctx.softmax_scale, ctx.causal, grads)
 
 
 class FlashAttnVarlenFunc(torch.autograd.Function):
@@ -195,8 +210,10 @@ class FlashAttnVarlenQKVPackedFunc(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
-        dq, dk, dv = _varlen_backward(ctx, dout)
-        return torch.stack((dq, dk, dv), dim=1), None, None, None, None, None
+        q, k, v = ctx.saved_tensors[:3]
+        dqkv, views = _packed_like((q, k, v), 1)
+        _varlen_backward(ctx, dout, views)
+        return dqkv, None, None, None, None, None
 
 
 class FlashAttnVarlenKVPackedFunc(torch.autograd.Function):
@@ -213,8 +230,10 @@ class FlashAttnVarlenKVPackedFunc(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
-        dq, dk, dv = _varlen_backward(ctx, dout)
-        return dq, torch.stack((dk, dv), dim=1), None, None, None, None, None, None, None
+        q, k, v = ctx.saved_tensors[:3]
+        dkv, (dk, dv) = _packed_like((k, v), 1)
+        dq, _, _ = _varlen_backward(ctx, dout, (torch.empty_like(q), dk, dv))
+        return dq, dkv, None, None, None, None, None, None, None
 
 
 # --------------------------------------------------------------------------------------------

@@ -128,6 +128,23 @@ def test_packed_variants_match_unpacked(ext, d, causal):
     assert torch.equal(dkv[:, :, 0], dk3) and torch.equal(dkv[:, :, 1], dv3)
 
 
+def test_bwd_binding_writes_into_given_strided_gradients(ext):
+    b, s, h, d = 1, 130, 2, 64
+    gen = torch.Generator().manual_seed(21)
+    q, k, v, dout = (randn_half(gen, b, s, h, d).to(DEV) for _ in range(4))
+    out, lse = ext.fwd(q, k, v, d ** -0.5, True)
+    dq, dk, dv = ext.bwd(q, k, v, out, lse, dout, d ** -0.5, True)  # the reference's eight arguments
+    packed = torch.full((b, s, 3, h, d), float("nan"), dtype=torch.half, device=DEV)
+    views = packed.unbind(2)
+    got = ext.bwd(q, k, v, out, lse, dout, d ** -0.5, True, *views)
+    assert all(g.data_ptr() == w.data_ptr() for g, w in zip(got, views))  # written in place, nothing new
+    assert torch.equal(packed[:, :, 0], dq) and torch.equal(packed[:, :, 1], dk) and torch.equal(packed[:, :, 2], dv)
+    with pytest.raises(RuntimeError, match="shape"):
+        ext.bwd(q, k, v, out, lse, dout, d ** -0.5, True, packed[:, :-1, 0], views[1], views[2])
+    with pytest.raises(RuntimeError, match="float16"):
+        ext.bwd(q, k, v, out, lse, dout, d ** -0.5, True, views[0].float(), views[1], views[2])
+
+
 def _varlen_case(seed, lens_q, lens_k, h, hk, d):
     gen = torch.Generator().manual_seed(seed)
     cq = torch.tensor([0] + torch.tensor(lens_q).cumsum(0).tolist(), dtype=torch.int32)
