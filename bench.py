@@ -313,7 +313,9 @@ def run_sharded(args):
     (1) head-sharded forward + backward, 16/N heads per rank, no communication (strong scaling);
     (2) sequence-sharded forward: K/V split into N contiguous ranges, every rank attends all queries against
         its range, then the partial (O, LSE) are merged -- once with all_to_all_single + fa_combine (NCCL) and
-        once with the fused kernel that reads the peers' partials in place (fa_combine_gather).
+        once with the fused kernel that reads the peers' partials in place (fa_combine_gather);
+    (3) sequence-sharded backward: the ordinary backward kernels on the K/V range with the merged O / LSE, the
+        dQ shares summed with fa_sum_gather after an all-to-all or read from the peers in place.
     Times are CUDA events, max over ranks; rank 0 prints one JSON line per measurement."""
     import torch
     import torch.distributed as dist
@@ -390,6 +392,34 @@ def run_sharded(args):
             rec["peer_read_unavailable"] = repr(exc)[:300]
         if rank == 0:
             print(json.dumps(rec), flush=True)
+        # (3) sequence sharded backward: dK/dV of the shard locally, dQ shares summed across the ranks
+        out_all, lse_all = sp.sequence_parallel_forward(q, ks, vs, scale, True, gather_output=True)
+        do = torch.randn(1, s, h, d, device=dev, dtype=torch.half, generator=gq)
+        ms_b = timed(lambda: sp.sequence_parallel_backward(q, ks, vs, out_all, lse_all, do, scale, True))
+        rec = {"workload": "C5 sequence-sharded backward (dQ shares exchanged in fp16, summed in fp32)", "n_gpus": world,
+               "reduce_all_to_all_ms": ms_b, "bwd_tflops_all_to_all": 2.5 * f_fwd / ms_b / 1e9}
+        try:
+            dq_ref, _, _ = sp.sequence_parallel_backward(q, ks, vs, out_all, lse_all, do, scale, True)
+            dq_p2p, _, _ = sp.sequence_parallel_backward_p2p(q, ks, vs, out_all, lse_all, do, scale, True)
+            rec["p2p_vs_all_to_all_max_abs_diff"] = float((dq_p2p.float() - dq_ref.float()).abs().max().item())
+            ms_p = timed(lambda: sp.sequence_parallel_backward_p2p(q, ks, vs, out_all, lse_all, do, scale, True))
+            rec.update({"reduce_peer_read_ms": ms_p, "bwd_tflops_peer_read": 2.5 * f_fwd / ms_p / 1e9})
+            rec["partial_backward_ms"] = timed(
+                lambda: sp.partial_backward(q, ks, vs, out_all, lse_all, do, rank * shard, scale, True))
+        except Exception as exc:  # noqa: BLE001  symmetric memory not usable here
+            rec["peer_read_unavailable"] = repr(exc)[:300]
+        if rank == 0:
+            print(json.dumps(rec), flush=True)
+        # (4) the same two with the zig-zag layout (two chunks per rank: equal causal work on every rank)
+        del out_all, lse_all
+        ms_zf = timed(lambda: sp.sequence_parallel_forward(q, ks, vs, scale, True, layout="zigzag"))
+        out_all, lse_all = sp.sequence_parallel_forward(q, ks, vs, scale, True, gather_output=True, layout="zigzag")
+        ms_zb = timed(lambda: sp.sequence_parallel_backward(q, ks, vs, out_all, lse_all, do, scale, True,
+                                                             layout="zigzag"))
+        if rank == 0:
+            print(json.dumps({"workload": "C5 sequence-sharded, zig-zag K/V chunks (balanced causal work), all-to-all exchange",
+                              "n_gpus": world, "fwd_ms": ms_zf, "fwd_tflops": f_fwd / ms_zf / 1e9, "bwd_ms": ms_zb,
+                              "bwd_tflops": 2.5 * f_fwd / ms_zb / 1e9}), flush=True)
     if rank == 0:
         print(json.dumps({"device_status": int(ext.device_status(True))}), flush=True)
     if world > 1:

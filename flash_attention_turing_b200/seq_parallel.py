@@ -17,6 +17,10 @@ rank.  Plumbing is ``torch.distributed`` (NCCL over NVLink on GPUs; gloo in the 
     all_to_all_single: query-row slice j of every rank's dq share -> rank j        (one collective)
     rank j:  dq[slice j] = sum of the shares of slice j                            (fa_sum_gather)
 
+With ``layout="zigzag"`` rank r holds chunks r and 2*world-1-r of 2*world equal chunks, which gives every
+rank the same amount of causal work (a contiguous range gives the last rank 2*world-1 times the work of
+the first); the rank merges (adds) the results of its two chunks locally before the exchange.
+
 In these paths no kernel reads peer memory: the collective lands the partials in local memory first.
 The ``*_p2p`` variants replace the collective by ONE kernel that reads the peers' buffers in place.
 
@@ -60,6 +64,42 @@ def _default_sum(shares):
     from . import _ext
 
     return _ext.load().sum_gather(list(shares.unbind(0)), 0, shares.shape[2])
+
+
+def _default_merge2(o_parts, lse_parts):
+    from . import _ext
+
+    return _ext.load().combine_gather(list(o_parts), list(lse_parts), 0, o_parts[0].shape[1])
+
+
+def _default_add2(parts):
+    from . import _ext
+
+    return _ext.load().sum_gather(list(parts), 0, parts[0].shape[1])
+
+
+def _check_layout(layout: str) -> bool:
+    if layout not in ("contiguous", "zigzag"):
+        raise ValueError("layout must be 'contiguous' or 'zigzag'")
+    return layout == "zigzag"
+
+
+def shard_chunks(rank: int, world: int, seqlen: int, layout: str = "contiguous"):
+    """Key ranges [(begin, end), ...] of rank ``rank``: one contiguous range, or the two zig-zag chunks."""
+    if _check_layout(layout):
+        if seqlen % (2 * world) != 0:
+            raise ValueError("seqlen_k must be divisible by twice the number of ranks for the zigzag layout")
+        c = seqlen // (2 * world)
+        return [(rank * c, (rank + 1) * c), ((2 * world - 1 - rank) * c, (2 * world - rank) * c)]
+    if seqlen % world != 0:
+        raise ValueError("seqlen_k must be divisible by the number of ranks")
+    c = seqlen // world
+    return [(rank * c, (rank + 1) * c)]
+
+
+def shard_kv(x: torch.Tensor, rank: int, world: int, layout: str = "contiguous") -> torch.Tensor:
+    """The rows of x (b, s, h_k, d) that rank ``rank`` holds, concatenated in the order of ``shard_chunks``."""
+    return torch.cat([x[:, b:e] for b, e in shard_chunks(rank, world, x.shape[1], layout)], dim=1).contiguous()
 
 
 def partial_attention(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, key_offset: int,
@@ -128,17 +168,41 @@ def merge_partials(o_part: torch.Tensor, lse_part: torch.Tensor, group: Optional
     return out.to(o_part.dtype), lse
 
 
+def rank_partial(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, rank: int, world: int,
+                 softmax_scale: float, causal: bool, layout: str = "contiguous", fwd: Optional[FwdFn] = None,
+                 merge2=None, out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None):
+    """This rank's partial (O, LSE) for all query rows: ``partial_attention`` on its range, or on each of its
+    two zig-zag chunks followed by a local log-sum-exp merge of the two (``fa_combine_gather`` with two
+    local parts by default)."""
+    if not _check_layout(layout):
+        return partial_attention(q, k_shard, v_shard, rank * k_shard.shape[1], softmax_scale, causal, fwd, out, lse)
+    c = k_shard.shape[1] // 2
+    parts = [partial_attention(q, k_shard[:, i * c:(i + 1) * c], v_shard[:, i * c:(i + 1) * c], off, softmax_scale,
+                               causal, fwd)
+             for i, off in enumerate((rank * c, (2 * world - 1 - rank) * c))]
+    o, l = (merge2 or _default_merge2)([p[0] for p in parts], [p[1] for p in parts])
+    # rows that saw no key in either chunk: the merge reports LSE 0 there, the exchange wants -inf
+    dead = torch.isinf(parts[0][1]) & torch.isinf(parts[1][1])
+    l = torch.where(dead, torch.full_like(l, float("-inf")), l)
+    if out is not None:
+        out.copy_(o)
+        lse.copy_(l)
+        return out, lse
+    return o.to(q.dtype), l
+
+
 def sequence_parallel_forward(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor,
                               softmax_scale: Optional[float] = None, causal: bool = False,
                               group: Optional[dist.ProcessGroup] = None, gather_output: bool = False,
-                              fwd: Optional[FwdFn] = None, combine: Optional[CombineFn] = None):
-    """Forward with K/V sharded over the ranks of ``group`` by contiguous sequence ranges of equal length
-    (rank r holds keys [r * s_shard, (r + 1) * s_shard)); q is replicated.  Returns (out, lse) for this
-    rank's query-row slice, or for all rows when ``gather_output`` is set."""
+                              fwd: Optional[FwdFn] = None, combine: Optional[CombineFn] = None,
+                              layout: str = "contiguous", merge2=None):
+    """Forward with K/V sharded over the ranks of ``group`` (``shard_kv``: equal contiguous ranges, rank r
+    holding keys [r * s_shard, (r + 1) * s_shard), or zig-zag chunk pairs); q is replicated.  Returns
+    (out, lse) for this rank's query-row slice, or for all rows when ``gather_output`` is set."""
     rank = dist.get_rank(group)
     world = dist.get_world_size(group)
     scale = q.shape[-1] ** -0.5 if softmax_scale is None else softmax_scale
-    o_part, lse_part = partial_attention(q, k_shard, v_shard, rank * k_shard.shape[1], scale, causal, fwd)
+    o_part, lse_part = rank_partial(q, k_shard, v_shard, rank, world, scale, causal, layout, fwd, merge2)
     out, lse = merge_partials(o_part, lse_part, group, combine)
     if not gather_output:
         return out, lse
@@ -172,7 +236,7 @@ def _p2p_buffers(shape_o, shape_l, dtype, device, group):
 
 def sequence_parallel_forward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor,
                                   softmax_scale: Optional[float] = None, causal: bool = False,
-                                  group: Optional[dist.ProcessGroup] = None):
+                                  group: Optional[dist.ProcessGroup] = None, layout: str = "contiguous"):
     """Same result as ``sequence_parallel_forward`` (this rank's query-row slice), but without the
     all-to-all: the partials are written into symmetric memory, a device-side barrier orders the ranks,
     and ONE kernel (``fa_combine_gather``) reads the query-row slice of every rank's partial straight from
@@ -188,7 +252,7 @@ def sequence_parallel_forward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_shar
         raise ValueError("seqlen_q must be divisible by the number of ranks")
     scale = d ** -0.5 if softmax_scale is None else softmax_scale
     o_buf, l_buf, hdl_o, hdl_l = _p2p_buffers(q.shape, (b, h, s), q.dtype, q.device, group)
-    partial_attention(q, k_shard, v_shard, rank * k_shard.shape[1], scale, causal, None, o_buf, l_buf)
+    rank_partial(q, k_shard, v_shard, rank, world, scale, causal, layout, None, None, o_buf, l_buf)
     hdl_o.barrier(channel=0)  # every rank's partial is complete and visible
     o_parts = [hdl_o.get_buffer(r, q.shape, q.dtype) for r in range(world)]
     l_parts = [hdl_l.get_buffer(r, (b, h, s), torch.float32) for r in range(world)]
@@ -247,6 +311,26 @@ def partial_backward(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tens
     return dq_share, dk.to(k_shard.dtype), dv.to(v_shard.dtype)
 
 
+def rank_backward(q, k_shard, v_shard, out, lse, dout, rank: int, world: int, softmax_scale: float, causal: bool,
+                  layout: str = "contiguous", bwd: Optional[BwdFn] = None, add2=None,
+                  dq_share: Optional[torch.Tensor] = None):
+    """This rank's (dq share for all rows, dk_shard, dv_shard): ``partial_backward`` on its range, or on each
+    of its two zig-zag chunks with the two dQ shares added (``fa_sum_gather`` with two local parts by
+    default) and dK / dV concatenated in shard order."""
+    if not _check_layout(layout):
+        return partial_backward(q, k_shard, v_shard, out, lse, dout, rank * k_shard.shape[1], softmax_scale, causal,
+                                bwd, dq_share)
+    c = k_shard.shape[1] // 2
+    res = [partial_backward(q, k_shard[:, i * c:(i + 1) * c], v_shard[:, i * c:(i + 1) * c], out, lse, dout, off,
+                            softmax_scale, causal, bwd)
+           for i, off in enumerate((rank * c, (2 * world - 1 - rank) * c))]
+    dq = (add2 or _default_add2)([r[0] for r in res])
+    if dq_share is not None:
+        dq_share.copy_(dq)
+        dq = dq_share
+    return dq.to(q.dtype), torch.cat([r[1] for r in res], dim=1), torch.cat([r[2] for r in res], dim=1)
+
+
 def reduce_dq_shares(dq_share: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
                      sum_parts: Optional[SumFn] = None) -> torch.Tensor:
     """Exchange and sum.  dq_share (b, s, h, d) is this rank's share for ALL query rows; returns this rank's
@@ -267,20 +351,23 @@ def reduce_dq_shares(dq_share: torch.Tensor, group: Optional[dist.ProcessGroup] 
 def sequence_parallel_backward(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, out: torch.Tensor,
                                lse: torch.Tensor, dout: torch.Tensor, softmax_scale: Optional[float] = None,
                                causal: bool = False, group: Optional[dist.ProcessGroup] = None,
-                               bwd: Optional[BwdFn] = None, sum_parts: Optional[SumFn] = None):
+                               bwd: Optional[BwdFn] = None, sum_parts: Optional[SumFn] = None,
+                               layout: str = "contiguous", add2=None):
     """Backward of ``sequence_parallel_forward``.  q, dout and the merged out (b, s, h, d) / lse (b, h, s) are
     replicated (all query rows on every rank, e.g. from ``gather_output=True``); K/V are sharded as in the
     forward.  Returns (dq for this rank's query-row slice (b, s / world, h, d), dk_shard, dv_shard)."""
     rank = dist.get_rank(group)
+    world = dist.get_world_size(group)
     scale = q.shape[-1] ** -0.5 if softmax_scale is None else softmax_scale
-    dq_share, dk, dv = partial_backward(q, k_shard, v_shard, out, lse, dout, rank * k_shard.shape[1], scale, causal,
-                                        bwd)
+    dq_share, dk, dv = rank_backward(q, k_shard, v_shard, out, lse, dout, rank, world, scale, causal, layout, bwd,
+                                     add2)
     return reduce_dq_shares(dq_share, group, sum_parts), dk, dv
 
 
 def sequence_parallel_backward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, out: torch.Tensor,
                                    lse: torch.Tensor, dout: torch.Tensor, softmax_scale: Optional[float] = None,
-                                   causal: bool = False, group: Optional[dist.ProcessGroup] = None):
+                                   causal: bool = False, group: Optional[dist.ProcessGroup] = None,
+                                   layout: str = "contiguous"):
     """Same result as ``sequence_parallel_backward`` without the all-to-all: the dQ shares are written into
     symmetric memory, a device-side barrier orders the ranks, and ONE kernel (``fa_sum_gather``) reads the
     query-row slice of every rank's share straight from that rank's HBM over NVLink (plain loads, no
@@ -295,7 +382,7 @@ def sequence_parallel_backward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_sha
         raise ValueError("seqlen_q must be divisible by the number of ranks")
     scale = d ** -0.5 if softmax_scale is None else softmax_scale
     buf, _, hdl, _ = _p2p_buffers(q.shape, (b, h, s), q.dtype, q.device, group)
-    _, dk, dv = partial_backward(q, k_shard, v_shard, out, lse, dout, rank * k_shard.shape[1], scale, causal, None, buf)
+    _, dk, dv = rank_backward(q, k_shard, v_shard, out, lse, dout, rank, world, scale, causal, layout, None, None, buf)
     hdl.barrier(channel=0)  # every rank's share is complete and visible
     parts = [hdl.get_buffer(r, q.shape, q.dtype) for r in range(world)]
     sl = s // world

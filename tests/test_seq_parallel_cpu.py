@@ -156,3 +156,69 @@ def test_partial_backward_rows_before_the_shard_get_no_gradient():
     assert dq[:, 8:].abs().max().item() > 0
     rq, rk, rv = orc.attention_backward(q, k, v, dout, 0.125, True)
     assert (dk - rk[:, 8:12]).abs().max().item() < 1e-5 and (dv - rv[:, 8:12]).abs().max().item() < 1e-5
+
+
+# ------------------------------------------------------------------------------------------------
+# zig-zag layout: two chunks per rank, merged locally before the exchange
+# ------------------------------------------------------------------------------------------------
+def _oracle_merge2(o_parts, lse_parts):
+    b, s, h, d = o_parts[0].shape
+    o_acc = torch.stack([o.float().permute(0, 2, 1, 3).reshape(b * h * s, d) for o in o_parts])
+    l_acc = torch.stack([l.reshape(b * h * s) for l in lse_parts])
+    out, lse = orc.combine(o_acc, l_acc)
+    return out.view(b, h, s, d).permute(0, 2, 1, 3).contiguous(), lse.view(b, h, s)
+
+
+def _oracle_add2(parts):
+    return parts[0].float() + parts[1].float()
+
+
+def _zigzag_worker(rank, world, port, causal, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from flash_attention_turing_b200 import seq_parallel as sp
+
+        torch.manual_seed(13)
+        b, s, h, hk, d = 1, 64, 4, 2, 64
+        q, dout = torch.randn(b, s, h, d), torch.randn(b, s, h, d)
+        k, v = torch.randn(b, s, hk, d), torch.randn(b, s, hk, d)
+        ks, vs = sp.shard_kv(k, rank, world, "zigzag"), sp.shard_kv(v, rank, world, "zigzag")
+        out, lse = sp.sequence_parallel_forward(q, ks, vs, None, causal, gather_output=True, fwd=_oracle_fwd,
+                                                combine=_oracle_combine, layout="zigzag", merge2=_oracle_merge2)
+        dq, dk, dv = sp.sequence_parallel_backward(q, ks, vs, out, lse, dout, None, causal, bwd=_oracle_bwd,
+                                                   sum_parts=_oracle_sum, layout="zigzag", add2=_oracle_add2)
+        ref_out, ref_lse = orc.attention_forward(q, k, v, None, causal)
+        rq, rk, rv = orc.attention_backward(q, k, v, dout, None, causal)
+        sl = s // world
+        results[rank] = ((out - ref_out).abs().max().item(), (lse - ref_lse).abs().max().item(),
+                         (dq - rq[:, rank * sl:(rank + 1) * sl]).abs().max().item(),
+                         (dk - sp.shard_kv(rk, rank, world, "zigzag")).abs().max().item(),
+                         (dv - sp.shard_kv(rv, rank, world, "zigzag")).abs().max().item())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("causal", [False, True])
+def test_zigzag_layout_matches_single_process(world, causal):
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_zigzag_worker, args=(world, _free_port(), causal, results), nprocs=world, join=True)
+    assert len(results) == world
+    for rank in range(world):
+        assert max(results[rank]) < 2e-5, (rank, results[rank])
+
+
+def test_shard_chunks():
+    from flash_attention_turing_b200 import seq_parallel as sp
+
+    assert sp.shard_chunks(1, 4, 64) == [(16, 32)]
+    assert sp.shard_chunks(1, 4, 64, "zigzag") == [(8, 16), (48, 56)]
+    covered = sorted(c for r in range(4) for c in sp.shard_chunks(r, 4, 64, "zigzag"))
+    assert covered == [(8 * i, 8 * i + 8) for i in range(8)]
+    with pytest.raises(ValueError):
+        sp.shard_chunks(0, 4, 36, "zigzag")
+    with pytest.raises(ValueError):
+        sp.shard_chunks(0, 4, 64, "striped")

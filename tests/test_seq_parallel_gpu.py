@@ -78,7 +78,7 @@ def test_two_gpu_sequence_parallel_forward(causal, d):
         assert err_one <= 3e-3, (rank, err_one)
 
 
-def _bwd_worker(rank, world, port, causal, d, results):
+def _bwd_worker(rank, world, port, causal, d, results, layout="contiguous"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -96,26 +96,26 @@ def _bwd_worker(rank, world, port, causal, d, results):
         k = torch.randn(b, s, hk, d, generator=gen).half()
         v = torch.randn(b, s, hk, d, generator=gen).half()
         dout = torch.randn(b, s, h, d, generator=gen).half()
-        shard = s // world
         sl = s // world
         qd, dod = q.to(dev), dout.to(dev)
-        ks = k[:, rank * shard:(rank + 1) * shard].contiguous().to(dev)
-        vs = v[:, rank * shard:(rank + 1) * shard].contiguous().to(dev)
-        out, lse = sp.sequence_parallel_forward(qd, ks, vs, None, causal, gather_output=True)
-        dq, dk, dv = sp.sequence_parallel_backward(qd, ks, vs, out, lse, dod, None, causal)
+        ks, vs = sp.shard_kv(k, rank, world, layout).to(dev), sp.shard_kv(v, rank, world, layout).to(dev)
+        out, lse = sp.sequence_parallel_forward(qd, ks, vs, None, causal, gather_output=True, layout=layout)
+        dq, dk, dv = sp.sequence_parallel_backward(qd, ks, vs, out, lse, dod, None, causal, layout=layout)
         torch.cuda.synchronize()
         p2p_err = -1.0
         try:
-            dq_p, dk_p, dv_p = sp.sequence_parallel_backward_p2p(qd, ks, vs, out, lse, dod, None, causal)
+            dq_p, dk_p, dv_p = sp.sequence_parallel_backward_p2p(qd, ks, vs, out, lse, dod, None, causal, layout=layout)
             torch.cuda.synchronize()
             p2p_err = max((dq_p.float() - dq.float()).abs().max().item(), (dk_p.float() - dk.float()).abs().max().item(),
                           (dv_p.float() - dv.float()).abs().max().item())
         except (ImportError, RuntimeError) as exc:  # symmetric memory not usable on this box
             print("p2p path unavailable:", exc)
         rq, rk, rv = orc.attention_backward(q, k, v, dout, None, causal)
+        ref_out, _ = orc.attention_forward(q, k, v, None, causal)
         errs = ((dq.float().cpu() - rq[:, rank * sl:(rank + 1) * sl]).abs().max().item(),
-                (dk.float().cpu() - rk[:, rank * shard:(rank + 1) * shard]).abs().max().item(),
-                (dv.float().cpu() - rv[:, rank * shard:(rank + 1) * shard]).abs().max().item())
+                (dk.float().cpu() - sp.shard_kv(rk, rank, world, layout)).abs().max().item(),
+                (dv.float().cpu() - sp.shard_kv(rv, rank, world, layout)).abs().max().item(),
+                (out.float().cpu() - ref_out).abs().max().item())
         scale = max(rq.abs().max().item(), rk.abs().max().item(), rv.abs().max().item())
         results[rank] = (errs, scale, int(ext.device_status(True)), p2p_err)
     finally:
@@ -137,3 +137,19 @@ def test_two_gpu_sequence_parallel_backward(causal, d):
         assert p2p_err <= 1e-6, (rank, p2p_err)  # same kernels, same order of additions; -1 when unavailable
         # fp16 gradients, the dQ shares rounded to fp16 before they are summed
         assert max(errs) <= 4e-3 + 2.0 ** -9 * scale, (rank, errs, scale)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_two_gpu_zigzag_layout_forward_and_backward(d):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_bwd_worker, args=(world, _free_port(), True, d, results, "zigzag"), nprocs=world, join=True)
+    for rank in range(world):
+        errs, scale, status, p2p_err = results[rank]
+        assert status == 0
+        assert p2p_err <= 1e-6, (rank, p2p_err)
+        # one more fp16 rounding than the contiguous layout: the two chunks' results are merged locally
+        assert max(errs) <= 5e-3 + 2.0 ** -9 * scale, (rank, errs, scale)
