@@ -645,15 +645,13 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
     const float* stats = sStats + cq * 32;
     int i_rel = 0;  // Q tile within the current head
     bool ok = true;
-    bool st_ready = false;  // probe of st_full for the coming tile
     for (int it = 0; it < n_it; ++it) {
       const int ss = it & 1;
-      if (!(ok = warp_wait_unless(st_ready, &bars->st_full[ss], (it >> 1) & 1, ctx))) break;
+      if (!(ok = mbar_wait_warp(&bars->st_full[ss], (it >> 1) & 1, ctx))) break;
       if (!(ok = mbar_wait_warp(&bars->s_full, it & 1, ctx))) break;
       tc_fence_after_sync();
       uint32_t sr[32];
       tmem_ld32(tA, sr);
-      const bool p_free_ready = it == 0 || warp_probe(&bars->p_free, (it - 1) & 1);
       tmem_wait_ld();
       warp_arrive_loaded(&bars->s_loaded, lane);  // region A may now receive dP^T
       const float4* st_lse = reinterpret_cast<const float4*>(stats + ss * 256);
@@ -680,16 +678,13 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
 #pragma unroll
       for (int e = 0; e < 16; ++e) pk[e] = pack_half2(pr[e].x, pr[e].y);
       // the dV MMAs of the previous tile must have consumed the old P^T before it is overwritten
-      if (!(ok = warp_wait_unless(p_free_ready, &bars->p_free, (it - 1) & 1, ctx))) break;
+      if (it > 0 && !(ok = mbar_wait_warp(&bars->p_free, (it - 1) & 1, ctx))) break;
       tmem_st16(tP, pk);
-      const bool dp_ready = warp_probe(&bars->dp_full, it & 1);  // dP^T(it) ran under the exponentials
       warp_arrive(&bars->p_full, lane);
 
-      if (!(ok = warp_wait_unless(dp_ready, &bars->dp_full, it & 1, ctx))) break;
+      if (!(ok = mbar_wait_warp(&bars->dp_full, it & 1, ctx))) break;
       tc_fence_after_sync();
       tmem_ld32(tA, sr);
-      const bool ds_free_ready = it == 0 || warp_probe(&bars->ds_free[0], (it - 1) & 1);
-      st_ready = it + 1 < n_it && warp_probe(&bars->st_full[ss ^ 1], ((it + 1) >> 1) & 1);
       tmem_wait_ld();
       warp_arrive_loaded(&bars->dp_loaded, lane);  // region A may now receive the next S^T
 #pragma unroll
@@ -705,7 +700,7 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
       // the statistics of this tile are in use no longer
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->st_empty[ss]);
-      if (!(ok = warp_wait_unless(ds_free_ready, &bars->ds_free[0], (it - 1) & 1, ctx))) break;
+      if (it > 0 && !(ok = mbar_wait_warp(&bars->ds_free[0], (it - 1) & 1, ctx))) break;
       tmem_st16(tP + 64, pk);  // packed dS^T
       warp_arrive(&bars->ds_full, lane);
     }
