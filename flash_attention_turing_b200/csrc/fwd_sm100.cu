@@ -154,7 +154,49 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  if (threadIdx.x == 0) {
+  // The TMA producer thread initialises the barriers itself and issues the loads of the Q tiles and of the
+  // first K/V blocks BEFORE the CTA-wide synchronisation, so that their latency overlaps the TMEM
+  // allocation and the synchronisation instead of following them.
+  WaitCtx ctx{&bars->abort_flag, p.status};
+  auto load_q = [&]() {
+#pragma unroll
+    for (int t = 0; t < kTiles; ++t) {
+      if (nb[t] > 0) {
+        mbar_arrive_expect_tx(&bars->q_full[t], C::kTileBytes);
+#pragma unroll
+        for (int c = 0; c < C::kChunks; ++c)
+          tma_load_4d(sQ + t * C::kTileBytes + c * C::kChunkBytes, &p.tm_q, &bars->q_full[t],
+                      c * 64, head, q_off + row0 + t * kBlockM, bq);
+      }
+    }
+  };
+  auto load_kv = [&](int j) -> bool {
+    const int s = j % C::kStages;
+    const uint32_t ph = (j / C::kStages) & 1;
+    int krow = k_off + j * kBlockN;
+    int kb = bk;
+    if (p.block_table) {
+      const int tok = j * kBlockN;
+      kb = p.block_table[batch * p.block_table_batch_stride + tok / p.page_size];
+      krow = tok % p.page_size;
+    }
+    if (!mbar_wait(&bars->k_empty[s], ph ^ 1, ctx)) return false;
+    mbar_arrive_expect_tx(&bars->k_full[s], C::kTileBytes);
+#pragma unroll
+    for (int c = 0; c < C::kChunks; ++c)
+      tma_load_4d(sK + s * C::kTileBytes + c * C::kChunkBytes, &p.tm_k, &bars->k_full[s],
+                  c * 64, head_k, krow, kb);
+    if (!mbar_wait(&bars->v_empty[s], ph ^ 1, ctx)) return false;
+    mbar_arrive_expect_tx(&bars->v_full[s], C::kTileBytes);
+#pragma unroll
+    for (int c = 0; c < C::kChunks; ++c)
+      tma_load_4d(sV + s * C::kTileBytes + c * C::kChunkBytes, &p.tm_v, &bars->v_full[s],
+                  c * 64, head_k, krow, kb);
+    return true;
+  };
+  const int n_early = min(nb_max, C::kStages);  // their stages are free from the start: no wait blocks
+
+  if (warp == kProducerWarp && lane == 0) {
 #pragma unroll
     for (int t = 0; t < kTiles; ++t) {
       mbar_init(&bars->q_full[t], 1);
@@ -173,58 +215,23 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
     mbar_init(&bars->v_fixed, 1);
     bars->abort_flag = 0;
     fence_mbar_init();
+    load_q();
+    for (int j = 0; j < n_early; ++j) load_kv(j);
   }
   if (warp == kMmaWarp) {
     tmem_alloc(&bars->tmem_base, C::kTmemCols);
     tmem_relinquish();
   }
-  if (warp == kProducerWarp && lane == 0) {
-    prefetch_tensormap(&p.tm_q);
-    prefetch_tensormap(&p.tm_k);
-    prefetch_tensormap(&p.tm_v);
-  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
-  WaitCtx ctx{&bars->abort_flag, p.status};
 
   if (warp == kProducerWarp) {
     // =========================== TMA producer ===========================
     if (lane == 0) {
-#pragma unroll
-      for (int t = 0; t < kTiles; ++t) {
-        if (nb[t] > 0) {
-          mbar_arrive_expect_tx(&bars->q_full[t], C::kTileBytes);
-#pragma unroll
-          for (int c = 0; c < C::kChunks; ++c)
-            tma_load_4d(sQ + t * C::kTileBytes + c * C::kChunkBytes, &p.tm_q, &bars->q_full[t],
-                        c * 64, head, q_off + row0 + t * kBlockM, bq);
-        }
-      }
-      for (int j = 0; j < nb_max; ++j) {
-        const int s = j % C::kStages;
-        const uint32_t ph = (j / C::kStages) & 1;
-        int krow = k_off + j * kBlockN;
-        int kb = bk;
-        if (p.block_table) {
-          const int tok = j * kBlockN;
-          kb = p.block_table[batch * p.block_table_batch_stride + tok / p.page_size];
-          krow = tok % p.page_size;
-        }
-        if (!mbar_wait(&bars->k_empty[s], ph ^ 1, ctx)) break;
-        mbar_arrive_expect_tx(&bars->k_full[s], C::kTileBytes);
-#pragma unroll
-        for (int c = 0; c < C::kChunks; ++c)
-          tma_load_4d(sK + s * C::kTileBytes + c * C::kChunkBytes, &p.tm_k, &bars->k_full[s],
-                      c * 64, head_k, krow, kb);
-        if (!mbar_wait(&bars->v_empty[s], ph ^ 1, ctx)) break;
-        mbar_arrive_expect_tx(&bars->v_full[s], C::kTileBytes);
-#pragma unroll
-        for (int c = 0; c < C::kChunks; ++c)
-          tma_load_4d(sV + s * C::kTileBytes + c * C::kChunkBytes, &p.tm_v, &bars->v_full[s],
-                      c * 64, head_k, krow, kb);
-      }
+      for (int j = n_early; j < nb_max; ++j)
+        if (!load_kv(j)) break;
     }
     __syncwarp();
     if (fix_v_tail) {
