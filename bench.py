@@ -45,7 +45,7 @@ FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=
 # (dram__bytes_read.sum + dram__bytes_write.sum, one pass; summary in profiles/dram_traffic_full_size.md).
 # They are constants of the workload, not measured by this script; algorithmic tensor bytes for comparison:
 # forward 1078 MB, backward 3494 MB, decode 4275 MB.
-NCU_TRAFFIC_BYTES = dict(fwd=1058.7e6, bwd=548.3e6 + 1333.3e6 + 1587.6e6, decode=4286.8e6 + 4.5e6)
+NCU_TRAFFIC_BYTES = dict(fwd=1057.6e6, bwd=548.5e6 + 1333.0e6 + 1588.8e6, decode=4285.1e6 + 4.5e6)
 
 
 def fwd_flops(b, h, sq, sk, d, causal):
