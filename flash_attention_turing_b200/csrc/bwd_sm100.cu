@@ -19,8 +19,9 @@
 // TMEM columns.  dQ kernel: S [0,128), dP [128,256), dQ [256,256+D), packed dS double-buffered in
 // [384,448) / [448,512).  dK/dV kernel: one 128-column accumulator region A [0,128) that holds S^T and
 // then dP^T of the same Q tile in turn, packed P^T [128,192) and dS^T [192,256), dV [256,256+D),
-// dK [256+D,256+2D).  A region is handed back to the MMA warp as soon as its values sit in registers, so
-// the next S / dP / S^T is computed while the elementwise warps are still busy with the current tile.
+// dK [256+D,256+2D) (at D = 64 columns 384-511 are left over and dP^T gets them as a region of its own).
+// A region is handed back to the MMA warp as soon as its values sit in registers, so the next S / dP /
+// S^T is computed while the elementwise warps are still busy with the current tile.
 //
 // Replaces flash_bwd_dot_do_o_kernel (csrc/flash_attn/src/flash_bwd_preprocess_kernel.h:23-96),
 // compute_dq_1rowblock and compute_dk_dv_1colblock (src/flash_bwd_kernel.h:25-609, 613-1344) and
@@ -42,6 +43,11 @@ constexpr int kColS = 0;
 constexpr int kColDP = 128;
 constexpr int kColAcc = 256;
 constexpr int kColPacked = 384;  // dQ kernel: packed dS, two buffers of 64 columns
+// dK/dV kernel: columns of dP^T.  At D = 128 the accumulators fill columns 256-511 and dP^T has to share
+// region A with S^T; at D = 64 columns 384-511 are free, dP^T gets a region of its own and S^T(it+1) need
+// not wait until dP^T(it) has been read.
+template <int D>
+constexpr int kColDPT = (D == 64) ? 384 : kColS;
 __device__ __forceinline__ float2 exp2_pair(float2 x) { return make_float2(ex2f(x.x), ex2f(x.y)); }
 
 struct BwdKernelParams {
@@ -606,18 +612,25 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
       auto do_tile = [&](int it) { return smem_u32(sdO + (it % C::kStagesDO) * C::kTileBytes); };
       auto q_full = [&](int it) { return wait(&bars->a_full[it % C::kStagesQ], (it / C::kStagesQ) & 1); };
       auto do_full = [&](int it) { return wait(&bars->b_full[it % C::kStagesDO], (it / C::kStagesDO) & 1); };
-      const uint32_t tA = tmem_base + kColS;
+      const uint32_t tA = tmem_base + kColS, tA2 = tmem_base + kColDPT<D>;
+      constexpr bool kSharedRegion = kColDPT<D> == kColS;
       bool ok = wait(&bars->fixed_full, 0) && q_full(0);
       for (int it = 0; ok && it < n_it; ++it) {
-        if (it > 0 && !(ok = wait(&bars->dp_loaded, (it - 1) & 1))) break;
+        // region A is free once its last content was read: dP^T(it-1) when the region is shared, S^T(it-1) otherwise
+        if (it > 0 && !(ok = wait(kSharedRegion ? &bars->dp_loaded : &bars->s_loaded, (it - 1) & 1))) break;
         tc_fence_after_sync();
         ok = gemm_ss<D>(tA, k_addr, q_tile(it), idesc_nn, [&] { return do_full(it); });  // S^T(it) = K Q^T
         if (!ok) break;
         tc_commit(&bars->s_full);
         tc_commit(&bars->a_empty[it % C::kStagesQ]);  // second reader: the dK MMAs of this tile
-        if (!(ok = wait(&bars->s_loaded, it & 1))) break;
+        // the region of dP^T is free once S^T(it) (shared) or dP^T(it-1) (own region) was read
+        if (kSharedRegion) {
+          if (!(ok = wait(&bars->s_loaded, it & 1))) break;
+        } else if (it > 0) {
+          if (!(ok = wait(&bars->dp_loaded, (it - 1) & 1))) break;
+        }
         tc_fence_after_sync();
-        ok = gemm_ss<D>(tA, v_addr, do_tile(it), idesc_nn,  // dP^T(it) = V dO^T
+        ok = gemm_ss<D>(tA2, v_addr, do_tile(it), idesc_nn,  // dP^T(it) = V dO^T
                         [&] { return it + 1 >= n_it || q_full(it + 1); });
         if (!ok) break;
         tc_commit(&bars->dp_full);
@@ -703,7 +716,7 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
 
       if (!(ok = mbar_wait_warp(&bars->dp_full, it & 1, ctx))) break;
       tc_fence_after_sync();
-      tmem_ld32(tA, sr);
+      tmem_ld32(tA + (kColDPT<D> - kColS), sr);
       tmem_wait_ld();
       warp_arrive_loaded(&bars->dp_loaded, lane);  // region A may now receive the next S^T
 #pragma unroll
