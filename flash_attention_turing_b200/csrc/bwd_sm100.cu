@@ -110,6 +110,9 @@ struct BBarriers {
                            // dQ kernel [u]: the dQ MMAs have consumed packed-dS buffer u
   uint64_t st_full[2];     // dK/dV kernel: row statistics (lse, delta) of a Q tile loaded
   uint64_t st_empty[2];    // ... and read by all elementwise warps
+  uint64_t tail_fixed[2];  // rows past the end of a packed sequence have been zeroed in an operand tile
+                           // (dK/dV kernel: one barrier per dO stage, so that the producer cannot run two
+                           // phases ahead of the waiting thread)
   uint64_t acc_full;       // final accumulators ready
   uint32_t tmem_base;
   int abort_flag;
@@ -137,6 +140,8 @@ __device__ __forceinline__ void init_barriers(BBarriers* bars, int stages, int a
   mbar_init(&bars->p_free, 1);
   mbar_init(&bars->ds_free[0], 1);
   mbar_init(&bars->ds_free[1], 1);
+  mbar_init(&bars->tail_fixed[0], 1);
+  mbar_init(&bars->tail_fixed[1], 1);
   mbar_init(&bars->acc_full, 1);
   bars->abort_flag = 0;
   fence_mbar_init();
@@ -186,6 +191,23 @@ __device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint32
 #pragma unroll
   for (int k = 0; k < 8; ++k)
     mma_ts(d_tmem, a_tmem + k * 8, mnmajor_slice(bd, k), idesc, (zero_init && k == 0) ? 0u : 1u);
+}
+
+// Rows of a packed (varlen) tensor past the end of a sequence belong to the NEXT sequence.  Their scores are
+// masked (P = 0, dS = 0 by selection), but as operand rows of an accumulating MMA they would still be
+// multiplied by those zeros, and 0 x NaN/Inf in a neighbour's data would poison this sequence's gradients.
+// Whole 128-byte row segments of the swizzled tile are zeroed (the swizzle only permutes 16-byte units
+// inside a row); executed by all lanes of one warp, visible to the tensor core after the fence.
+template <int D>
+__device__ __forceinline__ void zero_tile_rows_from(uint8_t* tile, int first_row, int lane) {
+  using C = BCfg<D>;
+  for (int idx = lane; idx < (kBlock - first_row) * C::kChunks * 8; idx += 32) {
+    const int r = first_row + idx / (C::kChunks * 8);
+    const int u = idx % (C::kChunks * 8);
+    *reinterpret_cast<uint4*>(tile + (u >> 3) * C::kChunkBytes + r * 128 + (u & 7) * 16) = make_uint4(0, 0, 0, 0);
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
 }
 
 // One warp's arrival on a barrier that counts warps: all lanes have finished their TMEM stores.
@@ -359,10 +381,20 @@ bwd_dq_kernel(const __grid_constant__ BwdKernelParams p) {
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
 
+  // the last K block of a packed sequence holds rows of the next sequence (see zero_tile_rows_from)
+  const bool fix_k_tail = varlen && (sk % kBlock) != 0 && nb == nkb && nb > 0;
   if (warp == kProducerWarp) {
     if (lane == 0) {
       for (int j = n_early; j < nb; ++j)
         if (!load_kv(j)) break;
+    }
+    __syncwarp();
+    if (fix_k_tail) {
+      const int j = nkb - 1, s = j % C::kStagesK;
+      if (mbar_wait_warp(&bars->a_full[s], (j / C::kStagesK) & 1, ctx)) {
+        zero_tile_rows_from<D>(sK + s * C::kTileBytes, sk - j * kBlock, lane);
+        if (lane == 0) mbar_arrive(&bars->tail_fixed[0]);
+      }
     }
   } else if (warp == kMmaWarp) {
     if (lane == 0 && nb > 0) {
@@ -404,6 +436,7 @@ bwd_dq_kernel(const __grid_constant__ BwdKernelParams p) {
         const int s = j % C::kStagesK;
         if (!(ok = mbar_wait(&bars->a_full[s], (j / C::kStagesK) & 1, ctx))) break;
         if (!(ok = mbar_wait(&bars->ds_full, j & 1, ctx))) break;
+        if (fix_k_tail && j == nkb - 1 && !(ok = mbar_wait(&bars->tail_fixed[0], 0, ctx))) break;
         tc_fence_after_sync();
         gemm_ts<D>(tmem_base + kColAcc, tmem_base + kColPacked + (j & 1) * 64, smem_u32(sK + s * C::kTileBytes),
                    idesc_acc, j == 0);
@@ -463,6 +496,13 @@ bwd_dq_kernel(const __grid_constant__ BwdKernelParams p) {
         const float2 d = fmul2(pr[i], fadd2(make_float2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1])), nd2));
         pk[i] = pack_half2(d.x, d.y);
       }
+      if (limit < 31) {  // by selection: dP of a masked column may be NaN/Inf (rows of the next sequence in V)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          if (2 * i > limit) pk[i] &= 0xffff0000u;
+          if (2 * i + 1 > limit) pk[i] &= 0x0000ffffu;
+        }
+      }
       // packed dS: 64 consecutive columns per block (16 per column quarter), two alternating buffers; the
       // buffer is free because S(j) was issued only after the dQ MMAs of block j-2 had consumed it
       tmem_st16(tmem_base + lane_base + kColPacked + (j & 1) * 64 + cq * 16, pk);
@@ -506,13 +546,15 @@ bwd_dq_kernel(const __grid_constant__ BwdKernelParams p) {
 // =============================================================================================
 // 3. dK/dV kernel
 // =============================================================================================
-template <int D>
+// kVarlen: the sequences are packed (cu_seqlens); only then can a Q tile hold rows of a neighbouring
+// sequence, and only that instantiation carries the code that guards against them.
+template <int D, bool kVarlen>
 __global__ void __launch_bounds__(kNumThreads, 1)
 bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
   using C = BCfg<D>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int batch = blockIdx.z, head_k = blockIdx.y, nblk = blockIdx.x;
-  const bool varlen = p.cu_seqlens_q != nullptr;
+  constexpr bool varlen = kVarlen;
   const int q_off = varlen ? p.cu_seqlens_q[batch] : 0;
   const int sq = varlen ? p.cu_seqlens_q[batch + 1] - q_off : p.seqlen_q;
   const int k_off = varlen ? p.cu_seqlens_k[batch] : 0;
@@ -595,10 +637,30 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
 
+  // the last Q / dO tile of a packed sequence holds rows of the next sequence (see zero_tile_rows_from)
+  const bool fix_q_tail = kVarlen && (sq % kBlock) != 0 && n_it > 0;
+  const int q_tail_rows = sq - (nq - 1) * kBlock;  // valid rows of the last Q tile
   if (warp == kProducerWarp) {
-    if (lane == 0) {
-      for (int it = n_early; it < n_it; ++it)
-        if (!load_q_do(it)) break;
+    if (!fix_q_tail) {
+      if (lane == 0) {
+        for (int it = n_early; it < n_it; ++it)
+          if (!load_q_do(it)) break;
+      }
+    } else {
+      // the whole warp walks the tiles: lane 0 issues the loads, all lanes zero the tails
+      for (int it = 0; it < n_it; ++it) {
+        bool loaded = true;
+        if (lane == 0 && it >= n_early) loaded = load_q_do(it);
+        if (!__shfl_sync(0xffffffffu, loaded, 0)) break;
+        if (it % per_head == per_head - 1) {  // the last Q tile of this head
+          const int sq_ = it % C::kStagesQ, sd = it % C::kStagesDO;
+          if (!mbar_wait_warp(&bars->a_full[sq_], (it / C::kStagesQ) & 1, ctx)) break;
+          if (!mbar_wait_warp(&bars->b_full[sd], (it / C::kStagesDO) & 1, ctx)) break;
+          zero_tile_rows_from<D>(sQ + sq_ * C::kTileBytes, q_tail_rows, lane);
+          zero_tile_rows_from<D>(sdO + sd * C::kTileBytes, q_tail_rows, lane);
+          if (lane == 0) mbar_arrive(&bars->tail_fixed[sd]);
+        }
+      }
     }
   } else if (warp == kMmaWarp) {
     if (lane == 0 && n_it > 0) {
@@ -644,10 +706,15 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
       const uint32_t tP = tmem_base + kColDP, tDS = tmem_base + kColDP + 64;
       const uint32_t tDV = tmem_base + kColAcc, tDK = tmem_base + kColAcc + D;
       bool ok = true;
+      uint32_t tail_phase = 0;  // bit sd: parity of the next tail_fixed[sd] phase to wait for
       for (int it = 0; ok && it < n_it; ++it) {
         const int sq_ = it % C::kStagesQ, sd = it % C::kStagesDO;
         if (!(ok = mbar_wait(&bars->b_full[sd], (it / C::kStagesDO) & 1, ctx))) break;
         if (!(ok = mbar_wait(&bars->p_full, it & 1, ctx))) break;
+        if (fix_q_tail && it % per_head == per_head - 1) {
+          if (!(ok = mbar_wait(&bars->tail_fixed[sd], (tail_phase >> sd) & 1, ctx))) break;
+          tail_phase ^= 1u << sd;
+        }
         tc_fence_after_sync();
         gemm_ts<D>(tDV, tP, smem_u32(sdO + sd * C::kTileBytes), idesc_acc, it == 0);
         tc_commit(&bars->b_empty[sd]);
@@ -675,6 +742,7 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
     // this thread's quarter below  key - (sk - sq) - (i * 128 + cq * 32)  are masked
     const int cmin0 = p.is_causal ? key - (sk - sq) - (i_min * kBlock + cq * 32) : 0;
     const float* stats = sStats + cq * 32;
+    const int cmax_last = fix_q_tail ? max(0, min(32, q_tail_rows - cq * 32)) : 32;  // valid columns in the last Q tile
     int i_rel = 0;  // Q tile within the current head
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
@@ -688,7 +756,11 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
       warp_arrive_loaded(&bars->s_loaded, lane);  // region A may now receive dP^T
       const float4* st_lse = reinterpret_cast<const float4*>(stats + ss * 256);
       const float4* st_delta = reinterpret_cast<const float4*>(stats + ss * 256 + 128);
-      const int cmin = cmin0 - i_rel * kBlock;  // columns below cmin are masked
+      // columns below cmin are masked by causality; columns from cmax on are query rows past the end of the
+      // sequence (last Q tile of a packed sequence).  Both clamped to [0, 32] and packed into one register.
+      const int cmask = max(0, min(32, cmin0 - i_rel * kBlock)) |
+                        (((kVarlen && i_rel == per_head - 1) ? cmax_last : 32) << 8);
+      const bool col_masked = cmask != (32 << 8);
       if (++i_rel == per_head) i_rel = 0;
       float2 pr[16];
       uint32_t pk[16];
@@ -700,11 +772,12 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
         pr[2 * e + 1] = exp2_pair(ffma2(make_float2(__uint_as_float(sr[4 * e + 2]), __uint_as_float(sr[4 * e + 3])),
                                         c2, make_float2(l.z, l.w)));
       }
-      if (cmin > 0) {
+      if (col_masked) {
+        const int cmin = cmask & 0xff, cmax = cmask >> 8;
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          if (2 * e < cmin) pr[e].x = 0.f;
-          if (2 * e + 1 < cmin) pr[e].y = 0.f;
+          if (2 * e < cmin || 2 * e >= cmax) pr[e].x = 0.f;
+          if (2 * e + 1 < cmin || 2 * e + 1 >= cmax) pr[e].y = 0.f;
         }
       }
 #pragma unroll
@@ -728,6 +801,14 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
                                                      make_float2(dl.z, dl.w)));
         pk[2 * e] = pack_half2(d0.x, d0.y);
         pk[2 * e + 1] = pack_half2(d1.x, d1.y);
+      }
+      if (col_masked) {  // by selection: dP^T of a masked column may be NaN/Inf (dO rows of the next sequence)
+        const int cmin = cmask & 0xff, cmax = cmask >> 8;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          if (2 * e < cmin || 2 * e >= cmax) pk[e] &= 0xffff0000u;
+          if (2 * e + 1 < cmin || 2 * e + 1 >= cmax) pk[e] &= 0x0000ffffu;
+        }
       }
       // the statistics of this tile are in use no longer
       __syncwarp();
@@ -793,7 +874,8 @@ int launch_bwd(const BwdKernelParams& kp, const FaBwdParams* p, int stage_mask, 
   FA_CHECK_CUDA(cudaGetDevice(&dev));
   if (!configured[dev & 63]) {
     FA_CHECK_CUDA(cudaFuncSetAttribute(bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytesDq));
-    FA_CHECK_CUDA(cudaFuncSetAttribute(bwd_dkdv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytesDkdv));
+    FA_CHECK_CUDA(cudaFuncSetAttribute(bwd_dkdv_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytesDkdv));
+    FA_CHECK_CUDA(cudaFuncSetAttribute(bwd_dkdv_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytesDkdv));
     configured[dev & 63] = true;
   }
   if (stage_mask & 2) {
@@ -803,7 +885,10 @@ int launch_bwd(const BwdKernelParams& kp, const FaBwdParams* p, int stage_mask, 
   }
   if (stage_mask & 4) {
     dim3 grid_k((p->seqlen_k + kBlock - 1) / kBlock, p->h_k, p->b);
-    bwd_dkdv_kernel<D><<<grid_k, kNumThreads, C::kSmemBytesDkdv, stream>>>(kp);
+    if (kp.cu_seqlens_q != nullptr)
+      bwd_dkdv_kernel<D, true><<<grid_k, kNumThreads, C::kSmemBytesDkdv, stream>>>(kp);
+    else
+      bwd_dkdv_kernel<D, false><<<grid_k, kNumThreads, C::kSmemBytesDkdv, stream>>>(kp);
     FA_CHECK_CUDA(cudaGetLastError());
   }
   return FA_OK;

@@ -341,3 +341,32 @@ def test_c5_long_context_by_sampling(ext, d):
     p_last = torch.exp((q[0, -1].float() * k[0, -1].float()).sum(-1) * d ** -0.5 - lse[0, :, -1])
     want = p_last[:, None] * dout[0, -1].float()
     assert (dv[0, -1].float() - want).abs().max().item() <= 1e-3
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("lens,h,hk,d,poison", [([100, 300, 57], 4, 2, 128, 1), ([200, 64, 513], 2, 1, 64, 2),
+                                                ([130, 130, 130], 2, 2, 128, 0)])
+def test_varlen_gradients_ignore_nan_in_a_neighbouring_sequence(ext, lens, h, hk, d, poison, causal):
+    """The sequences of a packed batch are independent: NaN in every tensor of one sequence must not reach the
+    outputs or gradients of the others (rows of the next sequence share 128-row tiles with this one)."""
+    from flash_attention_turing_b200 import flash_attn_varlen_func
+
+    gen = torch.Generator().manual_seed(5)
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32)
+    total = int(cu[-1])
+    q, do = randn_half(gen, total, h, d), randn_half(gen, total, h, d)
+    k, v = randn_half(gen, total, hk, d), randn_half(gen, total, hk, d)
+    ro, _ = orc.varlen_forward(q, k, v, cu, cu, None, causal)
+    rq, rk, rv = orc.varlen_backward(q, k, v, do, cu, cu, None, causal)
+    lo, hi = int(cu[poison]), int(cu[poison + 1])
+    for t in (q, k, v, do):
+        t[lo:hi] = float("nan")
+    qd, kd, vd = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+    out = flash_attn_varlen_func(qd, kd, vd, cu.to(DEV), cu.to(DEV), max(lens), max(lens), causal=causal)
+    dq, dk, dv = torch.autograd.grad(out, (qd, kd, vd), do.to(DEV))
+    keep = torch.ones(total, dtype=torch.bool)
+    keep[lo:hi] = False
+    for name, got, want in (("O", out, ro), ("dQ", dq, rq), ("dK", dk, rk), ("dV", dv, rv)):
+        got = got.detach().float().cpu()[keep]
+        assert not torch.isnan(got).any(), name
+        _check(name, got, want[keep])
