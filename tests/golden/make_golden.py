@@ -1,8 +1,9 @@
 """Generates the golden fixtures in this directory by running the REFERENCE's own Python functions.
 
-Run in a container that has the reference checkout (default /root/reference, or $FA_REFERENCE_ROOT):
+Run where the reference checkout is present, giving its root as the argument or in
+$FA_REFERENCE_ROOT:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py <reference root>
 
 The reference's ``flash_attention_interface.py`` imports its CUDA extension at module import time;
 a stub module stands in for it (none of the functions used here touch the extension):
@@ -26,11 +27,13 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF_ROOT = os.environ.get("FA_REFERENCE_ROOT", "/root/reference")
+REF_ROOT = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FA_REFERENCE_ROOT")
 OUT_DIR = Path(__file__).resolve().parent
 
 
 def load_reference():
+    if not REF_ROOT or not Path(REF_ROOT, "flash_attention_interface.py").is_file():
+        raise SystemExit("give the root of the reference checkout as the argument or in $FA_REFERENCE_ROOT")
     sys.modules.setdefault("flash_attn_turing", types.ModuleType("flash_attn_turing"))
     sys.path.insert(0, REF_ROOT)
     import flash_attention_interface as ref  # noqa: E402
