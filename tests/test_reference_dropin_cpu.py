@@ -86,6 +86,29 @@ def test_reference_python_reaches_our_binding_and_is_refused_on_cpu(ref):
         ref.flash_attn_varlen_func(qv, qv, qv, cu, cu, 4, 4)
 
 
+def test_reference_helpers_bind_every_argument_of_our_bindings(ref):
+    """The reference's private helpers call ``bwd``, ``varlen_bwd`` and ``fwd_kvcache`` positionally
+    (``flash_attention_interface.py:42-51, 96-109, 131-152``).  With CPU tensors each call must get past
+    pybind's argument matching (no ``TypeError``: the reference would answer one from ``fwd_kvcache`` with
+    its legacy nine-argument call, ``:153-168``) and be refused by the binding's own device check."""
+    q = torch.randn(1, 4, 2, 64).half()
+    lse = torch.zeros(1, 2, 4)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        ref._flash_attn_backward(q, q, q, q, q, lse, 0.125, True)
+    cu = torch.tensor([0, 4], dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        ref._flash_attn_varlen_backward(q[0], q[0], q[0], q[0], q[0], lse, cu, cu, 4, 4, 0.125, True)
+    cache = torch.randn(1, 8, 2, 64).half()
+    lens = torch.tensor([4], dtype=torch.int32)
+    idx = torch.zeros(1, dtype=torch.int32)
+    for args in [(q, cache, cache, None, None, lens, None, None, 0.125, True, 0),
+                 (q, cache, cache, q[:, :1], q[:, :1], lens, idx, None, 0.125, True, 2),
+                 (q, torch.randn(2, 256, 2, 64).half(), torch.randn(2, 256, 2, 64).half(), None, None, lens, None,
+                  torch.zeros(1, 1, dtype=torch.int32), 0.125, True, 4)]:
+        with pytest.raises(RuntimeError, match="must be CUDA tensors"):
+            ref._flash_attn_kvcache_forward(*args)
+
+
 def _kvcache_cases():
     q = torch.randn(1, 2, 4, 64)
     kc, vc = torch.randn(1, 8, 2, 64), torch.randn(1, 8, 2, 64)
