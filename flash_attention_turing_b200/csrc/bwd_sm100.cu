@@ -262,45 +262,59 @@ struct PreParams {
   const int* cu_seqlens_q;
 };
 
-// grid (sq_pad / rows_per_block, h, b); each row is handled by d/8 threads (16-byte loads).
+// Work item = (group of kPreRows consecutive rows, head), heads fastest, d/8 threads per item (16-byte loads):
+// the threads of a block read neighbouring heads of the same rows, i.e. contiguous memory when the heads of a
+// row are adjacent, every thread has 2 * kPreRows loads in flight, and an item writes one full 32-byte sector
+// of each statistic.  grid (ceil(items / items_per_block), 1, b).
+constexpr int kPreRows = 8;
 __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreParams p) {
-  const int tpr = p.d / 8;  // threads per row: 8 or 16
-  const int rows_per_block = 256 / tpr;
-  const int row = blockIdx.x * rows_per_block + threadIdx.x / tpr;
+  const int tpr = p.d / 8;  // threads per item: 8 or 16
+  const int item = blockIdx.x * (256 / tpr) + threadIdx.x / tpr;
   const int sub = threadIdx.x % tpr;
-  const int head = blockIdx.y, batch = blockIdx.z;
+  const int head = item % p.h, row0 = (item / p.h) * kPreRows;
+  const int batch = blockIdx.z;
+  // items past the end take part in the shuffles and touch no memory (every access below is bounded)
   const int q_off = p.cu_seqlens_q ? p.cu_seqlens_q[batch] : 0;
   const int sq = p.cu_seqlens_q ? p.cu_seqlens_q[batch + 1] - q_off : p.seqlen_q;
-  float acc = 0.f;
-  if (row < sq) {
-    const int64_t o_idx = (p.cu_seqlens_q ? static_cast<int64_t>(q_off + row) * p.o_row_stride
-                                          : batch * p.o_batch_stride + static_cast<int64_t>(row) * p.o_row_stride) +
-                          head * p.o_head_stride + sub * 8;
-    const int64_t do_idx = (p.cu_seqlens_q ? static_cast<int64_t>(q_off + row) * p.do_row_stride
-                                           : batch * p.do_batch_stride + static_cast<int64_t>(row) * p.do_row_stride) +
-                           head * p.do_head_stride + sub * 8;
-    const uint4 a = *reinterpret_cast<const uint4*>(p.o + o_idx);
-    const uint4 b = *reinterpret_cast<const uint4*>(p.dout + do_idx);
-    const __half2* ah = reinterpret_cast<const __half2*>(&a);
-    const __half2* bh = reinterpret_cast<const __half2*>(&b);
+  const int64_t o_base = (p.cu_seqlens_q ? static_cast<int64_t>(q_off) * p.o_row_stride : batch * p.o_batch_stride) +
+                         head * p.o_head_stride + sub * 8;
+  const int64_t do_base = (p.cu_seqlens_q ? static_cast<int64_t>(q_off) * p.do_row_stride : batch * p.do_batch_stride) +
+                          head * p.do_head_stride + sub * 8;
+  uint4 a[kPreRows], b[kPreRows];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 x = __half22float2(ah[i]), y = __half22float2(bh[i]);
+  for (int i = 0; i < kPreRows; ++i) {
+    a[i] = make_uint4(0, 0, 0, 0);
+    b[i] = make_uint4(0, 0, 0, 0);
+    if (row0 + i < sq) {
+      a[i] = *reinterpret_cast<const uint4*>(p.o + o_base + static_cast<int64_t>(row0 + i) * p.o_row_stride);
+      b[i] = *reinterpret_cast<const uint4*>(p.dout + do_base + static_cast<int64_t>(row0 + i) * p.do_row_stride);
+    }
+  }
+  // lane `sub` of the item keeps the statistics of row `sub` (sub < kPreRows <= tpr)
+  const int64_t bh = static_cast<int64_t>(batch) * p.h + head;
+  float my_lse = 0.f;
+  if (sub < kPreRows && row0 + sub < sq) my_lse = p.lse[bh * p.lse_row_stride + row0 + sub];
+  float mine = 0.f;
+#pragma unroll
+  for (int i = 0; i < kPreRows; ++i) {
+    const __half2* ah = reinterpret_cast<const __half2*>(&a[i]);
+    const __half2* bh2 = reinterpret_cast<const __half2*>(&b[i]);
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 x = __half22float2(ah[k]), y = __half22float2(bh2[k]);
       acc = fmaf(x.x, y.x, acc);
       acc = fmaf(x.y, y.y, acc);
     }
+    // sum over the tpr (8 or 16) consecutive lanes of the item; every lane ends up with the total
+    for (int off = tpr / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (sub == i) mine = acc;
   }
-  // reduce over the tpr (8 or 16) consecutive lanes of the row
-  for (int off = tpr / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (sub == 0 && row < p.sq_pad) {
-    const int64_t idx = (static_cast<int64_t>(batch) * p.h + head) * p.sq_pad + row;
-    if (row < sq) {
-      p.delta[idx] = -acc;
-      p.lse2[idx] = -p.lse[(static_cast<int64_t>(batch) * p.h + head) * p.lse_row_stride + row] * kLog2e;
-    } else {
-      p.delta[idx] = 0.f;
-      p.lse2[idx] = -INFINITY;
-    }
+  if (sub < kPreRows && row0 + sub < p.sq_pad) {
+    const int64_t idx = bh * p.sq_pad + row0 + sub;
+    const bool valid = row0 + sub < sq;
+    p.delta[idx] = valid ? -mine : 0.f;
+    p.lse2[idx] = valid ? -my_lse * kLog2e : -INFINITY;
   }
 }
 
@@ -952,8 +966,9 @@ extern "C" int fa_bwd_stages(const FaBwdParams* p, int stage_mask, fa_stream_t s
   pp.lse_row_stride = p->lse_row_stride;
   pp.h = p->h; pp.seqlen_q = p->seqlen_q; pp.sq_pad = sq_pad; pp.d = p->d;
   pp.cu_seqlens_q = p->cu_seqlens_q;
-  const int rows_per_block = 256 / (p->d / 8);
-  dim3 grid_pre((sq_pad + rows_per_block - 1) / rows_per_block, p->h, p->b);
+  const int64_t pre_items = static_cast<int64_t>((sq_pad + kPreRows - 1) / kPreRows) * p->h;
+  const int items_per_block = 256 / (p->d / 8);
+  dim3 grid_pre(static_cast<unsigned>((pre_items + items_per_block - 1) / items_per_block), 1, p->b);
   if (stage_mask & 1) {
     bwd_preprocess_kernel<<<grid_pre, 256, 0, stream>>>(pp);
     FA_CHECK_CUDA(cudaGetLastError());
