@@ -149,10 +149,11 @@ def run_reference(args, rank: int):
     value = flops * args.steps / dt / 1e12
     sample = f"{slices} of {w['b'] * w['h']} (batch, head) slices per step, S={w['s']} D={w['d']} causal fwd+bwd"
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 0, "steps": args.steps,
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "H8K: B4 S8192 H32 D128 causal fwd+bwd", "sample": sample},
+        "config": {"workload": "H8K: B4 S8192 H32 D128 causal fwd+bwd", "sample": sample,
+                   "note": "CPU arm: rank 0 alone computes on the host cores at every N; no GPU is used"},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
