@@ -218,7 +218,7 @@ def run_profile_case(args):
 
 
 def run_all_configs(args):
-    """CUDA-event timings of the five configs of BASELINE.json on cuda:0 (forward, backward, decode).
+    """CUDA-event timings of the five benchmark configs on cuda:0 (forward, backward, decode).
     One JSON line per config; burst numbers (20 iterations each), not the sustained headline loop."""
     import torch
 
