@@ -110,9 +110,9 @@ struct BBarriers {
                            // dQ kernel [u]: the dQ MMAs have consumed packed-dS buffer u
   uint64_t st_full[2];     // dK/dV kernel: row statistics (lse, delta) of a Q tile loaded
   uint64_t st_empty[2];    // ... and read by all elementwise warps
-  uint64_t tail_fixed[2];  // rows past the end of a packed sequence have been zeroed in an operand tile
-                           // (dK/dV kernel: one barrier per dO stage, so that the producer cannot run two
-                           // phases ahead of the waiting thread)
+  uint64_t tail_fixed[4];  // rows past the end of a packed sequence have been zeroed in an operand tile
+                           // (dK/dV kernel: one barrier per dO stage -- up to 3 at head size 64 -- so that
+                           // the producer cannot run two phases ahead of the waiting thread)
   uint64_t acc_full;       // final accumulators ready
   uint32_t tmem_base;
   int abort_flag;
@@ -140,8 +140,7 @@ __device__ __forceinline__ void init_barriers(BBarriers* bars, int stages, int a
   mbar_init(&bars->p_free, 1);
   mbar_init(&bars->ds_free[0], 1);
   mbar_init(&bars->ds_free[1], 1);
-  mbar_init(&bars->tail_fixed[0], 1);
-  mbar_init(&bars->tail_fixed[1], 1);
+  for (int i = 0; i < 4; ++i) mbar_init(&bars->tail_fixed[i], 1);
   mbar_init(&bars->acc_full, 1);
   bars->abort_flag = 0;
   fence_mbar_init();

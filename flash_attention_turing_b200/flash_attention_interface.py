@@ -355,7 +355,7 @@ def flash_attn_with_kvcache(
         if k is not None:
             raise ValueError("cache_seqlens is required when appending k and v")
         cache_seqlens = capacity
-    if isinstance(cache_seqlens, int) and not isinstance(cache_seqlens, bool):
+    if isinstance(cache_seqlens, int):  # bool included, as in the reference (its :818)
         cache_seqlens = torch.full((batch,), cache_seqlens, dtype=torch.int32, device=k_cache.device)
     elif not isinstance(cache_seqlens, torch.Tensor):
         raise TypeError("cache_seqlens must be an int or a torch.Tensor")

@@ -216,22 +216,56 @@ def sequence_parallel_forward(q: torch.Tensor, k_shard: torch.Tensor, v_shard: t
 # ------------------------------------------------------------------------------------------------
 # Fused exchange + merge: every rank reads the other ranks' partials directly from their memory
 # ------------------------------------------------------------------------------------------------
-_P2P_BUFFERS = {}
+_P2P_BUFFERS: "OrderedDict" = None  # type: ignore[assignment]
+_P2P_MAX_SHAPES = 4  # symmetric buffers are kept for the most recently used shapes only
 
 
 def _p2p_buffers(shape_o, shape_l, dtype, device, group):
     """Symmetric-memory buffers for the partial (O, LSE) of one problem shape, allocated and exchanged once
-    per (shape, group) and reused.  Returns (o_buf, lse_buf, handle_o, handle_l)."""
+    per (shape, group) and reused; the least recently used shape is dropped beyond _P2P_MAX_SHAPES.
+    Returns (o_buf, lse_buf, handle_o, handle_l).  Collective: every rank of the group must call it with the
+    same arguments."""
     import torch.distributed._symmetric_memory as symm_mem
+    from collections import OrderedDict
 
+    global _P2P_BUFFERS
+    if _P2P_BUFFERS is None:
+        _P2P_BUFFERS = OrderedDict()
     group = group or dist.group.WORLD
     key = (tuple(shape_o), tuple(shape_l), dtype, str(device), group.group_name)
-    if key not in _P2P_BUFFERS:
-        o_buf = symm_mem.empty(*shape_o, dtype=dtype, device=device)
-        l_buf = symm_mem.empty(*shape_l, dtype=torch.float32, device=device)
-        _P2P_BUFFERS[key] = (o_buf, l_buf, symm_mem.rendezvous(o_buf, group.group_name),
-                             symm_mem.rendezvous(l_buf, group.group_name))
+    if key in _P2P_BUFFERS:
+        _P2P_BUFFERS.move_to_end(key)
+        return _P2P_BUFFERS[key]
+    o_buf = symm_mem.empty(*shape_o, dtype=dtype, device=device)
+    l_buf = symm_mem.empty(*shape_l, dtype=torch.float32, device=device)
+    _P2P_BUFFERS[key] = (o_buf, l_buf, symm_mem.rendezvous(o_buf, group.group_name),
+                         symm_mem.rendezvous(l_buf, group.group_name))
+    while len(_P2P_BUFFERS) > _P2P_MAX_SHAPES:
+        _P2P_BUFFERS.popitem(last=False)
     return _P2P_BUFFERS[key]
+
+
+def peer_memory_available(shape_o, shape_l, dtype, device, group: Optional[dist.ProcessGroup] = None) -> bool:
+    """Collective.  True iff EVERY rank of the group could allocate and map the symmetric buffers for this
+    problem shape.  The ranks agree on the answer with a host-side all-reduce, so that either all of them
+    take a ``*_p2p`` path (which waits for its peers on the device) or none does."""
+    ok = 1
+    try:
+        _p2p_buffers(shape_o, shape_l, dtype, device, group)
+    except (ImportError, RuntimeError, AttributeError) as exc:
+        ok = 0
+        _last_p2p_error[0] = f"{type(exc).__name__}: {exc}"
+    flag = torch.tensor([ok], dtype=torch.int32, device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    return bool(flag.item())
+
+
+_last_p2p_error = [""]
+
+
+def last_peer_memory_error() -> str:
+    """Why peer_memory_available() last said no on this rank ("" if it did not)."""
+    return _last_p2p_error[0]
 
 
 def sequence_parallel_forward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor,
@@ -251,14 +285,19 @@ def sequence_parallel_forward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_shar
     if s % world != 0:
         raise ValueError("seqlen_q must be divisible by the number of ranks")
     scale = d ** -0.5 if softmax_scale is None else softmax_scale
+    # Everything that can fail on the host -- allocation, rendezvous, mapping the peers' buffers, the local
+    # kernels' argument checks -- happens before the first device-side barrier; between the two barriers the
+    # merge runs under try/finally, so a rank that fails there still releases its peers.
     o_buf, l_buf, hdl_o, hdl_l = _p2p_buffers(q.shape, (b, h, s), q.dtype, q.device, group)
-    rank_partial(q, k_shard, v_shard, rank, world, scale, causal, layout, None, None, o_buf, l_buf)
-    hdl_o.barrier(channel=0)  # every rank's partial is complete and visible
     o_parts = [hdl_o.get_buffer(r, q.shape, q.dtype) for r in range(world)]
     l_parts = [hdl_l.get_buffer(r, (b, h, s), torch.float32) for r in range(world)]
+    rank_partial(q, k_shard, v_shard, rank, world, scale, causal, layout, None, None, o_buf, l_buf)
     sl = s // world
-    out, lse = ext.combine_gather(o_parts, l_parts, rank * sl, sl)
-    hdl_o.barrier(channel=1)  # nobody overwrites a partial that a peer is still reading
+    hdl_o.barrier(channel=0)  # every rank's partial is complete and visible
+    try:
+        out, lse = ext.combine_gather(o_parts, l_parts, rank * sl, sl)
+    finally:
+        hdl_o.barrier(channel=1)  # nobody overwrites a partial that a peer is still reading
     return out, lse
 
 
@@ -382,10 +421,12 @@ def sequence_parallel_backward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_sha
         raise ValueError("seqlen_q must be divisible by the number of ranks")
     scale = d ** -0.5 if softmax_scale is None else softmax_scale
     buf, _, hdl, _ = _p2p_buffers(q.shape, (b, h, s), q.dtype, q.device, group)
-    _, dk, dv = rank_backward(q, k_shard, v_shard, out, lse, dout, rank, world, scale, causal, layout, None, None, buf)
-    hdl.barrier(channel=0)  # every rank's share is complete and visible
     parts = [hdl.get_buffer(r, q.shape, q.dtype) for r in range(world)]
+    _, dk, dv = rank_backward(q, k_shard, v_shard, out, lse, dout, rank, world, scale, causal, layout, None, None, buf)
     sl = s // world
-    dq = ext.sum_gather(parts, rank * sl, sl)
-    hdl.barrier(channel=1)  # nobody overwrites a share that a peer is still reading
+    hdl.barrier(channel=0)  # every rank's share is complete and visible
+    try:
+        dq = ext.sum_gather(parts, rank * sl, sl)
+    finally:
+        hdl.barrier(channel=1)  # nobody overwrites a share that a peer is still reading
     return dq, dk, dv

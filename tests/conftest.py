@@ -19,6 +19,37 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: test needs a CUDA GPU (sm_100a) and the built extension")
 
 
+def pytest_sessionfinish(session, exitstatus):
+    """FA_PARITY_LOG=<file>: write every recorded parity comparison (see helpers.PARITY_LOG) as JSON lines."""
+    import json
+    import os
+
+    path = os.environ.get("FA_PARITY_LOG")
+    if not path:
+        return
+    try:
+        import helpers
+    except ImportError:
+        return
+    with open(path, "w") as f:
+        for rec in helpers.PARITY_LOG:
+            f.write(json.dumps(rec) + "\n")
+
+
+@pytest.fixture(autouse=True)
+def _parity_case_name(request):
+    """Prefix the records of helpers.PARITY_LOG with the id of the test that made them."""
+    try:
+        import helpers
+    except ImportError:
+        yield
+        return
+    n0 = len(helpers.PARITY_LOG)
+    yield
+    for rec in helpers.PARITY_LOG[n0:]:
+        rec["name"] = request.node.name + "/" + rec["name"]
+
+
 @pytest.fixture(scope="session")
 def ext():
     """The torch binding; importing it must not silently fall back to anything."""

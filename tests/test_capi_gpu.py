@@ -95,6 +95,49 @@ def test_fa_combine_raw():
     assert out.float().cpu().permute(0, 2, 1, 3).reshape(rows, d)[7].abs().max().item() == 0
 
 
+@pytest.mark.parametrize("n,b,s,h,d,row_begin,rows", [(2, 2, 10, 3, 64, 4, 5), (8, 1, 33, 2, 128, 0, 33),
+                                                    (5, 2, 16, 4, 128, 15, 1), (16, 1, 9, 1, 64, 2, 6)])
+def test_fa_combine_gather_raw_on_one_gpu(n, b, s, h, d, row_begin, rows):
+    """The merge of per-rank partials, here with all parts in this GPU's own memory (the kernel does not care
+    whose memory a part pointer names): 2 to 16 parts in the forward's layout, a row slice, empty parts
+    (LSE = -inf) whose O holds NaN and must not be read into the result, and one row that every part left
+    empty.  Expected values: the oracle's combine on the same slice."""
+    from flash_attention_turing_b200 import capi
+
+    lib = capi.lib()
+    gen = torch.Generator().manual_seed(100 + n)
+    o_parts = [torch.randn(b, s, h, d, generator=gen).half() for _ in range(n)]
+    l_parts = [torch.randn(b, h, s, generator=gen) * 3 for _ in range(n)]
+    l_parts[0][:, :, row_begin] = float("-inf")      # part 0 saw no key for the first row of the slice
+    o_parts[0][:, row_begin] = float("nan")
+    dead_row = row_begin + rows - 1
+    for r in range(n):                               # a row nobody saw a key for
+        l_parts[r][0, 0, dead_row] = float("-inf")
+        o_parts[r][0, dead_row, 0] = float("nan")
+    sl = slice(row_begin, row_begin + rows)
+    o_acc = torch.stack([torch.nan_to_num(x[:, sl].float()).permute(0, 2, 1, 3).reshape(-1, d) for x in o_parts])
+    l_acc = torch.stack([x[:, :, sl].reshape(-1) for x in l_parts])
+    want_o, want_l = orc.combine(o_acc, l_acc)                          # rows ordered (b, h, row)
+    od, ld = [x.to(DEV) for x in o_parts], [x.to(DEV) for x in l_parts]
+    out = torch.full((b, rows, h, d), float("nan"), dtype=torch.half, device=DEV)
+    lse = torch.full((b, h, rows), float("nan"), dtype=torch.float32, device=DEV)
+    p = capi.FaCombineGatherParams()
+    for i in range(n):
+        p.o_part[i], p.lse_part[i] = od[i].data_ptr(), ld[i].data_ptr()
+    p.o, p.lse = out.data_ptr(), lse.data_ptr()
+    p.num_parts, p.b, p.h, p.seqlen_q, p.d, p.row_begin, p.rows = n, b, h, s, d, row_begin, rows
+    capi.check(lib.fa_combine_gather(ctypes.byref(p), _stream()))
+    torch.cuda.synchronize()
+    got = out.float().cpu().permute(0, 2, 1, 3).reshape(-1, d)
+    assert not torch.isnan(got).any()
+    assert err_stats(got, want_o)[0] <= 2.0 ** -10 * max(1.0, want_o.abs().max().item())  # one fp16 rounding
+    assert err_stats(lse.view(-1), want_l)[0] <= 1e-5
+    assert out[0, rows - 1, 0].abs().max().item() == 0 and lse[0, 0, rows - 1].item() == 0
+    p.num_parts = 17
+    assert lib.fa_combine_gather(ctypes.byref(p), _stream()) != 0
+    assert lib.fa_device_status(1) == 0
+
+
 def test_fa_sum_gather_raw():
     from flash_attention_turing_b200 import capi
 

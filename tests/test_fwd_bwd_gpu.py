@@ -6,8 +6,9 @@ never reaches (all of its head pairs have Hq != Hk)."""
 import pytest
 import torch
 
-from helpers import (LSE_TOL, MAX_ABS_TOL, MEAN_ABS_TOL, emulated_reference_kernel_error, err_stats, load_golden,
-                     randn_half, t)
+from helpers import (LSE_TOL, assert_reference_suite_bounds, assert_within_twice_reference_kernel,
+                     emulate_reference_kernel, emulate_reference_kernel_one, emulate_reference_kernel_varlen,
+                     err_stats, load_golden, randn_half, t)
 from oracle import attention_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -24,19 +25,14 @@ def _inputs(seed, b, sq, sk, h, hk, d):
             randn_half(gen, b, sq, h, d))
 
 
-def _check(name, got, want, max_tol=MAX_ABS_TOL, mean_tol=MEAN_ABS_TOL):
-    """The reference's bounds are stated between two fp16 results; against the fp32 oracle an allowance
-    is added for the two fp16 roundings every such kernel has (the reference's included,
-    flash_fwd_kernel.h:578 and flash_bwd_kernel.h:439): P / dS before the second GEMM and the output
-    itself, half an ulp (2^-11 relative) each."""
-    mx, mean = err_stats(got, want)
-    wf = want.detach().float().abs()
-    if wf.numel():
-        max_tol = max_tol + 2.0 ** -10 * wf.max().item()
-        mean_tol = mean_tol + 2.0 ** -10 * wf.mean().item()
-    assert not torch.isnan(got).any(), f"{name}: NaN"
-    assert mx <= max_tol, f"{name}: max abs err {mx:.3e} > {max_tol:.1e}"
-    assert mean <= mean_tol, f"{name}: mean abs err {mean:.3e} > {mean_tol:.1e}"
+def _check(name, got, want, emul, absolute=True):
+    """The stated tolerance: error against the fp32 oracle within twice the error of the reference's CUDA
+    kernel on the same inputs (emulated rounding points, helpers.py).  ``absolute`` adds the reference
+    suite's own bounds (max 9e-3, mean 2e-4), which are meant for its grid of short sequences: at the
+    benchmark sizes |dK|, |dV| reach 16 and more, where half an fp16 ulp of the result alone is 8e-3."""
+    assert_within_twice_reference_kernel(name, got, want, emul)
+    if absolute:
+        assert_reference_suite_bounds(name, got, want, emul)
 
 
 @pytest.mark.parametrize("d", [64, 128])
@@ -56,22 +52,22 @@ def test_dense_forward_backward_grid(ext, d, causal, sq, sk):
     s = d ** -0.5 if scale is None else scale
     o_ref, _ = orc.attention_forward(q, k, v, s, causal)
     rq, rk, rv = orc.attention_backward(q, k, v, dout, s, causal)
-    _check("O", out, o_ref)
-    _check("dQ", dq, rq)
-    _check("dK", dk, rk)
-    _check("dV", dv, rv)
+    em = emulate_reference_kernel(q, k, v, dout, s, causal)
+    _check("O", out, o_ref, em.out)
+    _check("dQ", dq, rq, em.dq)
+    _check("dK", dk, rk, em.dk)
+    _check("dV", dv, rv, em.dv)
 
 
-@pytest.mark.parametrize("d,b,s,h,hk,causal", [(64, 2, 512, 8, 8, False), (128, 1, 1024, 4, 1, True)])
-def test_forward_error_within_twice_the_reference_kernels(ext, d, b, s, h, hk, causal):
-    # C1 of the benchmark configs (B2 S512 H8 D64 non-causal) and a causal GQA case: O within 2x the
-    # error of an emulation of the reference kernel's rounding points, LSE within 1e-3.
-    q, k, v, _ = _inputs(1001, b, s, s, h, hk, d)
-    out, lse = ext.fwd(q.to(DEV), k.to(DEV), v.to(DEV), d ** -0.5, causal)
-    o_ref, lse_ref = orc.attention_forward(q, k, v, None, causal)
-    ref_err = emulated_reference_kernel_error(q, k, v, d ** -0.5, causal, o_ref)
-    mx, _ = err_stats(out, o_ref)
-    assert mx <= 2 * ref_err + 1e-5, f"O err {mx:.3e} vs reference-kernel emulation {ref_err:.3e}"
+def test_c1_forward_full_size(ext):
+    # C1 of the benchmark configs: forward, non-causal, B2 S512 H8 D64, scale 1/sqrt(64); O and LSE of
+    # every (batch, head) against the oracle.
+    b, s, h, d = 2, 512, 8, 64
+    q, k, v, _ = _inputs(1001, b, s, s, h, h, d)
+    out, lse = ext.fwd(q.to(DEV), k.to(DEV), v.to(DEV), d ** -0.5, False)
+    o_ref, lse_ref = orc.attention_forward(q, k, v, None, False)
+    em = emulate_reference_kernel(q, k, v, None, d ** -0.5, False)
+    _check("O", out, o_ref, em.out)
     assert err_stats(lse, lse_ref)[0] <= LSE_TOL
 
 
@@ -89,11 +85,12 @@ def test_golden_fixtures(ext, name):
         want_out = torch.nan_to_num(t(g["out"])[b:b + 1], nan=0.0)
         want_lse = t(g["lse"])[b:b + 1]
         want_lse = torch.where(torch.isfinite(want_lse), want_lse, torch.zeros_like(want_lse))
-        _check("O", out, want_out)
+        em = emulate_reference_kernel(q[b:b + 1], k[b:b + 1, : lens[b]], v[b:b + 1, : lens[b]], dout[b:b + 1], scale, causal)
+        _check("O", out, want_out, em.out)
         assert err_stats(lse, want_lse)[0] <= LSE_TOL
-        _check("dQ", dq, t(g["dq"])[b:b + 1])
-        _check("dK", dk, t(g["dk"])[b:b + 1, : lens[b]])
-        _check("dV", dv, t(g["dv"])[b:b + 1, : lens[b]])
+        _check("dQ", dq, t(g["dq"])[b:b + 1], em.dq)
+        _check("dK", dk, t(g["dk"])[b:b + 1, : lens[b]], em.dk)
+        _check("dV", dv, t(g["dv"])[b:b + 1, : lens[b]], em.dv)
 
 
 @pytest.mark.parametrize("d", [64, 128])
@@ -113,7 +110,8 @@ def test_packed_variants_match_unpacked(ext, d, causal):
     assert torch.equal(out_p, out)  # same kernel, same data, strided vs contiguous: bit-identical
     assert torch.equal(dqkv[:, :, 0], dq) and torch.equal(dqkv[:, :, 1], dk) and torch.equal(dqkv[:, :, 2], dv)
     o_ref, _ = orc.attention_forward(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), None, causal)
-    _check("O", out_p, o_ref)
+    em = emulate_reference_kernel(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), None, d ** -0.5, causal)
+    _check("O", out_p, o_ref, em.out)
 
     hk = 2
     kv = randn_half(gen, b, s, 2, hk, d).to(DEV).requires_grad_(True)
@@ -171,10 +169,11 @@ def test_varlen_forward_backward(ext, d, causal, lens_q, lens_k, h, hk):
     dq, dk, dv = torch.autograd.grad(out, (qd, kd, vd), dout.to(DEV))
     o_ref, lses = orc.varlen_forward(q, k, v, cq, ck, None, causal)
     rq, rk, rv = orc.varlen_backward(q, k, v, dout, cq, ck, None, causal)
-    _check("O", out, o_ref)
-    _check("dQ", dq, rq)
-    _check("dK", dk, rk)
-    _check("dV", dv, rv)
+    em = emulate_reference_kernel_varlen(q, k, v, dout, cq, ck, d ** -0.5, causal)
+    _check("O", out, o_ref, em.out)
+    _check("dQ", dq, rq, em.dq)
+    _check("dK", dk, rk, em.dk)
+    _check("dV", dv, rv, em.dv)
     # padded LSE (b, h, max_seqlen_q): valid part matches, padding stays zero
     _, lse = ext.varlen_fwd(qd.detach(), kd.detach(), vd.detach(), cq.to(DEV), ck.to(DEV), max(lens_q), max(lens_k),
                             d ** -0.5, causal)
@@ -249,28 +248,36 @@ def test_binding_errors(ext):
         ext.fwd(q[0], k[0], k[0], 1.0, False)
 
 
-@pytest.mark.parametrize("causal", [True])
-def test_full_size_causal_config_by_sampling(ext, causal):
-    # C2 of the benchmark configs: B4 S4096 H32 D128 causal, forward + backward at full size.
-    # The fp32 oracle is evaluated on two (batch, head) slices; attention is independent per
-    # (batch, head), so a slice of the full-size launch must match the oracle of that slice.
-    b, s, h, d = 4, 4096, 32, 128
-    gen = torch.Generator(device=DEV).manual_seed(1002)
-    q, k, v, dout = (torch.randn(b, s, h, d, device=DEV, dtype=torch.half, generator=gen) for _ in range(4))
-    out, lse = ext.fwd(q, k, v, d ** -0.5, causal)
-    dq, dk, dv = ext.bwd(q, k, v, out, lse, dout, d ** -0.5, causal)
-    for bi, hi in [(0, 0), (3, 17)]:
+def _sampled_slices_check(q, k, v, dout, out, lse, dq, dk, dv, slices, causal=True):
+    """Attention is independent per (batch, head): a slice of a full-size launch must match the oracle of
+    that slice, within twice the reference kernel's error (emulated on the same slice)."""
+    d = q.shape[-1]
+    for bi, hi in slices:
         sl = lambda x: x[bi:bi + 1, :, hi:hi + 1].cpu()  # noqa: E731
         o_ref, lse_ref = orc.attention_forward(sl(q), sl(k), sl(v), None, causal)
         rq, rk, rv = orc.attention_backward(sl(q), sl(k), sl(v), sl(dout), None, causal)
-        _check("O", sl(out), o_ref)
+        em = emulate_reference_kernel(sl(q), sl(k), sl(v), sl(dout), d ** -0.5, causal)
+        _check("O", sl(out), o_ref, em.out, absolute=False)
         assert err_stats(lse[bi:bi + 1, hi:hi + 1], lse_ref)[0] <= LSE_TOL
-        _check("dQ", sl(dq), rq)
-        _check("dK", sl(dk), rk, max_tol=2 * MAX_ABS_TOL)  # grows with the number of summed rows
-        _check("dV", sl(dv), rv, max_tol=2 * MAX_ABS_TOL)
+        _check("dQ", sl(dq), rq, em.dq, absolute=False)
+        _check("dK", sl(dk), rk, em.dk, absolute=False)
+        _check("dV", sl(dv), rv, em.dv, absolute=False)
+
+
+@pytest.mark.parametrize("s", [4096, 8192])
+def test_full_size_causal_config_by_sampling(ext, s):
+    # S = 4096: C2 of the benchmark configs (B4 S4096 H32 D128 causal, forward + backward).  S = 8192: the
+    # shape the headline metric is quoted on.  Full-size launches; the oracle is evaluated on two
+    # (batch, head) slices.
+    b, h, d = 4, 32, 128
+    gen = torch.Generator(device=DEV).manual_seed(1002)
+    q, k, v, dout = (torch.randn(b, s, h, d, device=DEV, dtype=torch.half, generator=gen) for _ in range(4))
+    out, lse = ext.fwd(q, k, v, d ** -0.5, True)
+    dq, dk, dv = ext.bwd(q, k, v, out, lse, dout, d ** -0.5, True)
+    _sampled_slices_check(q, k, v, dout, out, lse, dq, dk, dv, [(0, 0), (3, 17)])
     # size-independent property: every softmax row sums to one => with V = 1, O = 1 exactly
     ones = torch.ones_like(v)
-    o1, _ = ext.fwd(q, k, ones, d ** -0.5, causal)
+    o1, _ = ext.fwd(q, k, ones, d ** -0.5, True)
     assert (o1.float() - 1).abs().max().item() <= 2e-3
 
 
@@ -308,37 +315,62 @@ def test_c3_gqa_varlen_full_size(ext):
         qs, ks, vs, ds = (x.detach()[a:b].cpu() for x in (q[:, hs], k[:, kv_head:kv_head + 1], v[:, kv_head:kv_head + 1], dout[:, hs]))
         o_ref, _ = orc.attention_forward_one(qs, ks, vs, d ** -0.5, True)
         rq, rk, rv = orc.attention_backward_one(qs, ks, vs, ds, d ** -0.5, True)
-        _check("O", out[a:b, hs], o_ref)
-        _check("dQ", dq[a:b, hs], rq)
-        _check("dK", dk[a:b, kv_head:kv_head + 1], rk, max_tol=2 * MAX_ABS_TOL)
-        _check("dV", dv[a:b, kv_head:kv_head + 1], rv, max_tol=2 * MAX_ABS_TOL)
+        em = emulate_reference_kernel_one(qs, ks, vs, ds, d ** -0.5, True)
+        _check("O", out[a:b, hs], o_ref, em.out, absolute=False)
+        _check("dQ", dq[a:b, hs], rq, em.dq, absolute=False)
+        _check("dK", dk[a:b, kv_head:kv_head + 1], rk, em.dk, absolute=False)
+        _check("dV", dv[a:b, kv_head:kv_head + 1], rv, em.dv, absolute=False)
 
 
 @pytest.mark.parametrize("d", [64, 128])
 def test_c5_long_context_by_sampling(ext, d):
     # C5: B1 S65536 H16 causal, forward + backward at full size on a head shard (2 of 16 heads, as one rank
-    # of an 8-GPU head-sharded run).  The oracle is evaluated on sampled query rows (forward) and through
-    # size-independent properties (backward): with V = 1 the output is 1, and the gradients of the
-    # linear functional sum(O * dO) must satisfy sum(dQ * Q) = sum(dK * K) (scores depend on Q K^T only).
+    # of an 8-GPU head-sharded run).  Causality makes exact value checks of the 65536-token launch cheap:
+    #   * rows [0, 8192) of O, LSE and dQ depend only on the first 8192 tokens: they must equal the oracle of
+    #     that prefix;
+    #   * dK, dV of the keys [61440, 65536) receive contributions from the query rows >= 61440 only: they must
+    #     equal the oracle evaluated on those 4096 query rows against all keys.
+    # Both within twice the reference kernel's (emulated) error; sampled rows and two identities on top.
     b, s, h = 1, 65536, 2
+    scale = d ** -0.5
     gen = torch.Generator(device=DEV).manual_seed(1005)
     q, k, v, dout = (torch.randn(b, s, h, d, device=DEV, dtype=torch.half, generator=gen) for _ in range(4))
-    out, lse = ext.fwd(q, k, v, d ** -0.5, True)
+    out, lse = ext.fwd(q, k, v, scale, True)
     rows = [0, 1, 127, 128, 4095, 30000, 65535]
     for r in rows:
         qs = q[:, r:r + 1, :1].cpu()
         o_ref, lse_ref = orc.attention_forward(qs, k[:, : r + 1, :1].cpu(), v[:, : r + 1, :1].cpu(), None, False)
-        assert err_stats(out[:, r:r + 1, :1], o_ref)[0] <= MAX_ABS_TOL
+        assert err_stats(out[:, r:r + 1, :1], o_ref)[0] <= 2e-3
         assert err_stats(lse[:, :1, r:r + 1], lse_ref)[0] <= LSE_TOL
-    o1, _ = ext.fwd(q, k, torch.ones_like(v), d ** -0.5, True)
+    o1, _ = ext.fwd(q, k, torch.ones_like(v), scale, True)
     assert (o1.float() - 1).abs().max().item() <= 2e-3
-    dq, dk, dv = ext.bwd(q, k, v, out, lse, dout, d ** -0.5, True)
+    dq, dk, dv = ext.bwd(q, k, v, out, lse, dout, scale, True)
     assert not any(torch.isnan(x).any().item() for x in (dq, dk, dv))
+    hd = 1  # the head that is compared value by value
+    one = lambda x, a, e: x[0, a:e, hd:hd + 1].cpu()  # noqa: E731
+    # prefix: the first 8192 tokens
+    n = 8192
+    qp, kp, vp, dp = (one(x, 0, n) for x in (q, k, v, dout))
+    o_ref, lse_ref = orc.attention_forward_one(qp, kp, vp, scale, True)
+    rq, _, _ = orc.attention_backward_one(qp, kp, vp, dp, scale, True)
+    em = emulate_reference_kernel_one(qp, kp, vp, dp, scale, True)
+    _check("O[:8192]", one(out, 0, n), o_ref, em.out, absolute=False)
+    assert err_stats(lse[0, hd:hd + 1, :n], lse_ref)[0] <= LSE_TOL
+    _check("dQ[:8192]", one(dq, 0, n), rq, em.dq, absolute=False)
+    # tail: the last 4096 query rows against all keys
+    r0 = s - 4096
+    qa, ka, va, da = (one(x, 0, s) for x in (q, k, v, dout))
+    rq, rk, rv = orc.attention_backward_one(qa, ka, va, da, scale, True, row_chunk=1024, row_start=r0)
+    em = emulate_reference_kernel_one(qa, ka, va, da, scale, True, row_chunk=1024, row_start=r0)
+    _check("dQ[-4096:]", one(dq, r0, s), rq[r0:], em.dq[r0:], absolute=False)
+    _check("dK[-4096:]", one(dk, r0, s), rk[r0:], em.dk[r0:], absolute=False)
+    _check("dV[-4096:]", one(dv, r0, s), rv[r0:], em.dv[r0:], absolute=False)
+    # identities over the whole launch: sum(dQ * Q) = sum(dK * K) (the scores depend on Q K^T only) ...
     lhs = (dq.float() * q.float()).sum().item()
     rhs = (dk.float() * k.float()).sum().item()
     assert abs(lhs - rhs) <= 2e-3 * max(abs(lhs), abs(rhs), (dq.float().abs() * q.float().abs()).sum().item() * 1e-3)
-    # dV of the last key row is exactly P[last query, last key] * dO[last query] = softmax weight of one element
-    p_last = torch.exp((q[0, -1].float() * k[0, -1].float()).sum(-1) * d ** -0.5 - lse[0, :, -1])
+    # ... and dV of the last key row is exactly P[last query, last key] * dO[last query]
+    p_last = torch.exp((q[0, -1].float() * k[0, -1].float()).sum(-1) * scale - lse[0, :, -1])
     want = p_last[:, None] * dout[0, -1].float()
     assert (dv[0, -1].float() - want).abs().max().item() <= 1e-3
 
@@ -358,6 +390,7 @@ def test_varlen_gradients_ignore_nan_in_a_neighbouring_sequence(ext, lens, h, hk
     k, v = randn_half(gen, total, hk, d), randn_half(gen, total, hk, d)
     ro, _ = orc.varlen_forward(q, k, v, cu, cu, None, causal)
     rq, rk, rv = orc.varlen_backward(q, k, v, do, cu, cu, None, causal)
+    em = emulate_reference_kernel_varlen(q, k, v, do, cu, cu, d ** -0.5, causal)
     lo, hi = int(cu[poison]), int(cu[poison + 1])
     for t in (q, k, v, do):
         t[lo:hi] = float("nan")
@@ -366,7 +399,80 @@ def test_varlen_gradients_ignore_nan_in_a_neighbouring_sequence(ext, lens, h, hk
     dq, dk, dv = torch.autograd.grad(out, (qd, kd, vd), do.to(DEV))
     keep = torch.ones(total, dtype=torch.bool)
     keep[lo:hi] = False
-    for name, got, want in (("O", out, ro), ("dQ", dq, rq), ("dK", dk, rk), ("dV", dv, rv)):
+    for name, got, want, emu in (("O", out, ro, em.out), ("dQ", dq, rq, em.dq), ("dK", dk, rk, em.dk), ("dV", dv, rv, em.dv)):
         got = got.detach().float().cpu()[keep]
         assert not torch.isnan(got).any(), name
-        _check(name, got, want[keep])
+        _check(name, got, want[keep], emu[keep])
+
+
+CANARY = 0x7BCD  # an fp16 bit pattern (finite, 6.2e4) that no kernel result takes by accident
+
+
+def _canary_view(shape, pad_elems=4096, dtype=torch.half):
+    """A tensor of `shape` cut out of a larger canary-filled buffer: `pad_elems` untouched elements before and
+    after, and a row pitch one head wider than needed, so that every (row) has a gap after its last head.
+    Returns (view, buffer, mask of the elements the view covers)."""
+    b, s, h, d = shape
+    pitch = (h + 1) * d
+    n = b * s * pitch
+    buf = torch.empty(n + 2 * pad_elems, dtype=dtype, device=DEV)
+    if dtype == torch.half:
+        buf.view(torch.int16).fill_(CANARY)
+    else:
+        buf.view(torch.int32).fill_(0x7BCD7BCD)
+    view = buf[pad_elems:pad_elems + n].view(b, s, h + 1, d)[:, :, :h]
+    mask = torch.zeros_like(buf, dtype=torch.bool)
+    mask[pad_elems:pad_elems + n].view(b, s, h + 1, d)[:, :, :h] = True
+    return view, buf, mask
+
+
+def _canaries_intact(buf, mask):
+    raw = buf.view(torch.int16) if buf.dtype == torch.half else buf.view(torch.int32)
+    want = CANARY if buf.dtype == torch.half else 0x7BCD7BCD
+    return bool((raw[~mask] == want).all().item())
+
+
+@pytest.mark.parametrize("b,sq,sk,h,hk,d,causal", [(2, 129, 257, 4, 2, 64, True), (1, 385, 131, 3, 1, 128, False),
+                                                   (2, 1, 300, 2, 2, 128, True), (1, 700, 700, 6, 3, 64, True)])
+def test_guard_bands_around_outputs_and_scratch(b, sq, sk, h, hk, d, causal):
+    """Nothing is written outside the tensors the caller handed over: O, LSE, dQ, dK, dV and the backward
+    scratch are cut out of canary-filled buffers (pads before and after, a gap after every row) through the
+    C ABI's strides, and the canaries are intact after forward and backward at odd sizes.  (The memory
+    checker of the CUDA toolkit is not available on the test machines.)"""
+    import ctypes
+
+    from flash_attention_turing_b200 import capi
+
+    lib = capi.lib()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    q, k, v, dout = (x.to(DEV) for x in _inputs(5 + sq, b, sq, sk, h, hk, d))
+    o, o_buf, o_mask = _canary_view((b, sq, h, d))
+    dq, dq_buf, dq_mask = _canary_view((b, sq, h, d))
+    dk, dk_buf, dk_mask = _canary_view((b, sk, hk, d))
+    dv, dv_buf, dv_mask = _canary_view((b, sk, hk, d))
+    lse_buf = torch.empty(b * h * sq + 2048, dtype=torch.float32, device=DEV)
+    lse_buf.view(torch.int32).fill_(0x7BCD7BCD)
+    lse = lse_buf[1024:1024 + b * h * sq].view(b, h, sq)
+    scale = d ** -0.5
+    capi.check(lib.fa_fwd(ctypes.byref(capi.fwd_params(q, k, v, o, lse, scale, causal)), stream))
+    bp = capi.bwd_params(q, k, v, o, dout, lse, dq, dk, dv, None, scale, causal)
+    need = lib.fa_bwd_workspace_bytes(ctypes.byref(bp))
+    ws_buf = torch.empty(need + 8192, dtype=torch.uint8, device=DEV)
+    ws_buf.fill_(0xA5)
+    bp.workspace, bp.workspace_bytes = ws_buf.data_ptr() + 4096, need
+    capi.check(lib.fa_bwd(ctypes.byref(bp), stream))
+    torch.cuda.synchronize()
+    for name, buf, mask in (("O", o_buf, o_mask), ("dQ", dq_buf, dq_mask), ("dK", dk_buf, dk_mask), ("dV", dv_buf, dv_mask)):
+        assert _canaries_intact(buf, mask), f"{name}: a write outside the tensor"
+    raw = lse_buf.view(torch.int32)
+    assert bool((raw[:1024] == 0x7BCD7BCD).all()) and bool((raw[1024 + b * h * sq:] == 0x7BCD7BCD).all()), "LSE"
+    assert bool((ws_buf[:4096] == 0xA5).all()) and bool((ws_buf[4096 + need:] == 0xA5).all()), "backward scratch"
+    # and the results inside are the right ones
+    qc, kc, vc, dc = (x.cpu() for x in (q, k, v, dout))
+    o_ref, lse_ref = orc.attention_forward(qc, kc, vc, None, causal)
+    rq, rk, rv = orc.attention_backward(qc, kc, vc, dc, None, causal)
+    em = emulate_reference_kernel(qc, kc, vc, dc, scale, causal)
+    for name, got, want, emu in (("O", o, o_ref, em.out), ("dQ", dq, rq, em.dq), ("dK", dk, rk, em.dk), ("dV", dv, rv, em.dv)):
+        _check(name, got, want, emu)
+    assert err_stats(lse, lse_ref)[0] <= LSE_TOL
+    assert lib.fa_device_status(1) == 0

@@ -11,6 +11,14 @@ import torch.multiprocessing as mp
 pytestmark = pytest.mark.gpu
 
 
+def _require_peer_path(errs, tol):
+    """The fused peer-read path ran on every rank and agrees with the all-to-all path; when the peers' memory
+    cannot be mapped on this machine the test says so as a skip instead of passing silently."""
+    if any(e < 0 for e in errs):
+        pytest.skip("symmetric memory unavailable: the fused peer-read path was not exercised")
+    assert max(errs) <= tol, errs
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -40,16 +48,16 @@ def _worker(rank, world, port, causal, d, results):
         vs = v[:, rank * shard:(rank + 1) * shard].contiguous().to(dev)
         out, lse = sp.sequence_parallel_forward(qd, ks, vs, None, causal, gather_output=True)
         torch.cuda.synchronize()
-        # fused exchange + merge over peer memory must give the same slice as the all-to-all path
+        # fused exchange + merge over peer memory must give the same slice as the all-to-all path; whether
+        # symmetric memory can be used is agreed on by all ranks on the host BEFORE anyone enters a device-side
+        # barrier, so that no rank waits for a peer that gave up
         p2p_err = -1.0
-        try:
+        if sp.peer_memory_available(qd.shape, (b, h, s), qd.dtype, dev):
             out_p, lse_p = sp.sequence_parallel_forward_p2p(qd, ks, vs, None, causal)
             torch.cuda.synchronize()
             sl = s // world
             p2p_err = max((out_p.float() - out[:, rank * sl:(rank + 1) * sl].float()).abs().max().item(),
                           (lse_p - lse[:, :, rank * sl:(rank + 1) * sl]).abs().max().item())
-        except (ImportError, RuntimeError) as exc:  # symmetric memory not usable on this box
-            print("p2p path unavailable:", exc)
         ref_out, ref_lse = orc.attention_forward(q, k, v, None, causal)
         one_out, _ = ext.fwd(qd, k.to(dev), v.to(dev), d ** -0.5, causal)
         results[rank] = ((out.float().cpu() - ref_out).abs().max().item(),
@@ -71,11 +79,11 @@ def test_two_gpu_sequence_parallel_forward(causal, d):
     mp.spawn(_worker, args=(world, _free_port(), causal, d, results), nprocs=world, join=True)
     for rank in range(world):
         err_o, err_l, err_one, status, p2p_err = results[rank]
-        assert p2p_err <= 1e-3, (rank, p2p_err)  # -1 when symmetric memory is unavailable
         assert status == 0
         assert err_o <= 3e-3, (rank, err_o)       # fp16 partials merged: two fp16 roundings
         assert err_l <= 1e-3, (rank, err_l)
         assert err_one <= 3e-3, (rank, err_one)
+    _require_peer_path([results[r][4] for r in range(world)], 1e-3)
 
 
 def _bwd_worker(rank, world, port, causal, d, results, layout="contiguous"):
@@ -103,13 +111,11 @@ def _bwd_worker(rank, world, port, causal, d, results, layout="contiguous"):
         dq, dk, dv = sp.sequence_parallel_backward(qd, ks, vs, out, lse, dod, None, causal, layout=layout)
         torch.cuda.synchronize()
         p2p_err = -1.0
-        try:
+        if sp.peer_memory_available(qd.shape, (b, h, s), qd.dtype, dev):
             dq_p, dk_p, dv_p = sp.sequence_parallel_backward_p2p(qd, ks, vs, out, lse, dod, None, causal, layout=layout)
             torch.cuda.synchronize()
             p2p_err = max((dq_p.float() - dq.float()).abs().max().item(), (dk_p.float() - dk.float()).abs().max().item(),
                           (dv_p.float() - dv.float()).abs().max().item())
-        except (ImportError, RuntimeError) as exc:  # symmetric memory not usable on this box
-            print("p2p path unavailable:", exc)
         rq, rk, rv = orc.attention_backward(q, k, v, dout, None, causal)
         ref_out, _ = orc.attention_forward(q, k, v, None, causal)
         errs = ((dq.float().cpu() - rq[:, rank * sl:(rank + 1) * sl]).abs().max().item(),
@@ -134,9 +140,9 @@ def test_two_gpu_sequence_parallel_backward(causal, d):
     for rank in range(world):
         errs, scale, status, p2p_err = results[rank]
         assert status == 0
-        assert p2p_err <= 1e-6, (rank, p2p_err)  # same kernels, same order of additions; -1 when unavailable
         # fp16 gradients, the dQ shares rounded to fp16 before they are summed
         assert max(errs) <= 4e-3 + 2.0 ** -9 * scale, (rank, errs, scale)
+    _require_peer_path([results[r][3] for r in range(world)], 1e-6)  # same kernels, same order of additions
 
 
 @pytest.mark.parametrize("d", [64, 128])
@@ -150,6 +156,6 @@ def test_two_gpu_zigzag_layout_forward_and_backward(d):
     for rank in range(world):
         errs, scale, status, p2p_err = results[rank]
         assert status == 0
-        assert p2p_err <= 1e-6, (rank, p2p_err)
         # one more fp16 rounding than the contiguous layout: the two chunks' results are merged locally
         assert max(errs) <= 5e-3 + 2.0 ** -9 * scale, (rank, errs, scale)
+    _require_peer_path([results[r][3] for r in range(world)], 1e-6)

@@ -6,8 +6,8 @@ binding that can launch kernels but has no allocator.  For them the library keep
 in an array of its own image (32 MiB per GPU) and this entry point uses it.
 
 The test calls the entry point through the C ABI twice in a row and compares each result with
-fa_kvcache() given a caller-owned workspace: same kernels, so the outputs must agree to the tolerance the
-other KV-cache tests use (they are in fact bit-identical).  The second call reuses the scratch the first
+fa_kvcache() given a caller-owned workspace -- same kernels, so the outputs must agree to the tolerance the
+other KV-cache tests use (they are in fact bit-identical) -- and with the CPU oracle.  The second call reuses the scratch the first
 one left behind, on different inputs, which proves that stale contents do no harm.  It also checks that
 a request beyond the built-in limit is refused with an error code instead of being launched.
 
@@ -41,14 +41,14 @@ def _case(seed, b, h, hk, d, page, per, lens, splits):
     def params(k_cache, v_cache, out, lse):
         return capi.kvcache_params(q, k_cache, v_cache, kn, vn, out, lse, lens_d, table, d ** -0.5, True, splits)
 
-    return params, kc, vc, q
+    return params, kc, vc, q, kn, vn, table
 
 
 def _run_both(lib, stream, seed, lens, splits):
     from flash_attention_turing_b200 import capi
 
     b, h, hk, d, page, per = len(lens), 8, 2, 128, 256, 8
-    params, kc, vc, q = _case(seed, b, h, hk, d, page, per, lens, splits)
+    params, kc, vc, q, kn, vn, p2_table = _case(seed, b, h, hk, d, page, per, lens, splits)
     # existing entry point, caller-owned workspace
     kc1, vc1 = kc.clone(), vc.clone()
     o1, l1 = torch.empty_like(q), torch.empty(b, h, 1, dtype=torch.float32, device=DEV)
@@ -68,6 +68,15 @@ def _run_both(lib, stream, seed, lens, splits):
     assert (o2.float() - o1.float()).abs().max().item() <= O_TOL
     assert (l2 - l1).abs().max().item() <= LSE_TOL
     assert torch.equal(kc2, kc1) and torch.equal(vc2, vc1)  # the in-place append is the same too
+    # ... and against the CPU oracle, not only against the sibling entry point
+    from oracle import attention_oracle as orc
+
+    table = p2_table.cpu()
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    o_ref, lse_ref = orc.kvcache_forward(q.cpu(), kc.cpu(), vc.cpu(), kn.cpu(), vn.cpu(), lens_t, None, table,
+                                         d ** -0.5, True)
+    assert (o2.float().cpu() - o_ref).abs().max().item() <= O_TOL
+    assert (l2.cpu() - lse_ref).abs().max().item() <= LSE_TOL
 
 
 def test_noalloc_matches_fa_kvcache_on_two_calls_in_a_row():
