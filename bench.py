@@ -179,8 +179,10 @@ def run_profile_case(args):
         lse = torch.empty(b, h, s, device=dev, dtype=torch.float32)
         fp = capi.fwd_params(q, k, v, o, lse, d ** -0.5, True)
         bp = capi.bwd_params(q, k, v, o, dout, lse, dq, dk, dv, None, d ** -0.5, True)
+        bp.flags = args.bwd_flags
         ws = torch.empty(lib.fa_bwd_workspace_bytes(ctypes.byref(bp)), dtype=torch.uint8, device=dev)
         bp = capi.bwd_params(q, k, v, o, dout, lse, dq, dk, dv, ws, d ** -0.5, True)
+        bp.flags = args.bwd_flags
         capi.check(lib.fa_fwd(ctypes.byref(fp), stream))
         for _ in range(args.profile_iters):
             if args.profile == "fwd":
@@ -438,6 +440,8 @@ def main():
     ap.add_argument("--profile", choices=["fwd", "bwd", "decode"], default=None,
                     help="run a few launches of one kernel group on a reduced case and exit (for ncu captures)")
     ap.add_argument("--profile-iters", type=int, default=3)
+    ap.add_argument("--bwd-flags", type=int, default=0,
+                    help="flags of FaBwdParams for --profile bwd (1 = FA_BWD_SINGLE_KERNEL)")
     ap.add_argument("--sharded", action="store_true",
                     help="multi-GPU runs of the long-context config (B1 S65536 H16 D128 causal): head-sharded forward + "
                          "backward (no communication) and the sequence-sharded forward with its (O, LSE) merge")

@@ -28,7 +28,7 @@ LIB_PATH = PKG_DIR / "libfa_b200.so"
 EXT_NAME = "_fa_b200_torch"
 EXT_PATH = PKG_DIR / f"{EXT_NAME}.so"
 
-CUDA_SOURCES = ["common.cu", "fwd_sm100.cu", "bwd_sm100.cu", "kvcache_sm100.cu", "combine.cu"]
+CUDA_SOURCES = ["common.cu", "fwd_sm100.cu", "bwd_sm100.cu", "bwd_fused_sm100.cu", "kvcache_sm100.cu", "combine.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo", "--use_fast_math",

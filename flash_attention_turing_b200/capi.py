@@ -55,8 +55,11 @@ class FaBwdParams(C.Structure):
         + [("lse_row_stride", _i64), ("b", _i32), ("seqlen_q", _i32), ("seqlen_k", _i32), ("h", _i32),
            ("h_k", _i32), ("d", _i32), ("total_q", _i32), ("total_k", _i32), ("softmax_scale", _f32),
            ("is_causal", _i32), ("cu_seqlens_q", _vp), ("cu_seqlens_k", _vp), ("workspace", _vp),
-           ("workspace_bytes", _sz)]
+           ("workspace_bytes", _sz), ("flags", _i32), ("reserved0", _i32)]
     )
+
+
+FA_BWD_SINGLE_KERNEL = 1
 
 
 class FaKvcacheParams(C.Structure):

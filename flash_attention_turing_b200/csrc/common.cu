@@ -107,7 +107,7 @@ extern "C" {
 
 const char* fa_last_error(void) { return fa::last_error().c_str(); }
 
-int fa_abi_version(void) { return 1; }
+int fa_abi_version(void) { return 2; }
 
 int fa_device_status(int reset) {
   int* p = fa::device_status_ptr();

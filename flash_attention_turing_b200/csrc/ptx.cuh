@@ -101,6 +101,12 @@ __device__ __forceinline__ uint32_t mbar_test_nonblocking(uint64_t* bar, uint32_
 struct WaitCtx {
   volatile int* abort_flag;  // shared memory, 0 = running
   int* status;               // global status word (may be null)
+  // Diagnosis of a wait that gave up: the FIRST one to do so also stores, in bits 8-31 of the status word,
+  // `tag` (bits 8-15: which warp role waited) and the index of the barrier inside the kernel's barrier block
+  // (bits 16-23; 8-byte units from `base`).  Both optional.
+  int tag = 0;
+  const void* base = nullptr;
+  int iter = 0;  // loop iteration of the waiting role (bits 25-30), maintained by kernels that want it recorded
 };
 
 // Bounded wait on an mbarrier phase.  Returns false when the CTA is aborting (this wait or another
@@ -119,7 +125,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
         t0 = now;
       } else if (now - t0 > 4000000000ull) {
         *ctx.abort_flag = 1;
-        if (ctx.status) atomicOr(ctx.status, kStatusWaitTimeout);
+        if (ctx.status) {
+          int idx = 0;
+          if (ctx.base) idx = static_cast<int>((reinterpret_cast<const uint8_t*>(bar) - static_cast<const uint8_t*>(ctx.base)) >> 3) & 0xff;
+          atomicCAS(ctx.status, 0, kStatusWaitTimeout | ((ctx.tag & 0xff) << 8) | (idx << 16) | ((parity & 1) << 24) | ((ctx.iter & 0x3f) << 25));
+          atomicOr(ctx.status, kStatusWaitTimeout);
+        }
         return false;
       }
     }
@@ -312,6 +323,13 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 __device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.ld.sync.aligned.16x256b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr)
+               : "memory");
+}
+// x4 = 32 columns: r[4j .. 4j+3] as above for j = 0..3.
+__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                : "r"(taddr)
                : "memory");
 }

@@ -13,6 +13,9 @@
 
 namespace {
 
+int g_bwd_flags = 0;  // flags of FaBwdParams used by bwd / varlen_bwd (set_single_kernel_backward)
+
+
 void check_rc(int rc, const char* what) {
   TORCH_CHECK(rc == FA_OK, what, " failed (", rc, "): ", fa_last_error());
 }
@@ -199,6 +202,7 @@ std::vector<at::Tensor> mha_bwd(at::Tensor q, at::Tensor k, at::Tensor v, at::Te
   p.h = num_heads; p.h_k = num_heads_k; p.d = head_size;
   p.softmax_scale = static_cast<float>(softmax_scale);
   p.is_causal = is_causal;
+  p.flags = g_bwd_flags;
   const size_t ws = fa_bwd_workspace_bytes(&p);
   at::Tensor workspace = torch::empty({static_cast<int64_t>(ws)}, q.options().dtype(torch::kUInt8));
   p.workspace = workspace.data_ptr();
@@ -255,6 +259,7 @@ std::vector<at::Tensor> mha_varlen_bwd(at::Tensor q, at::Tensor k, at::Tensor v,
   p.is_causal = is_causal;
   p.cu_seqlens_q = cu_seqlens_q.data_ptr<int>();
   p.cu_seqlens_k = cu_seqlens_k.data_ptr<int>();
+  p.flags = g_bwd_flags;
   const size_t ws = fa_bwd_workspace_bytes(&p);
   at::Tensor workspace = torch::empty({static_cast<int64_t>(ws)}, q.options().dtype(torch::kUInt8));
   p.workspace = workspace.data_ptr();
@@ -490,6 +495,12 @@ at::Tensor sum_gather(std::vector<at::Tensor> parts, int64_t row_begin, int64_t 
 
 int64_t device_status(bool reset) { return fa_device_status(reset ? 1 : 0); }
 
+// Which backward path bwd / varlen_bwd use: false (default) = the dQ kernel + the dK/dV kernel, bitwise
+// reproducible; true = the single kernel with five products whose dQ accumulation order depends on scheduling
+// (FA_BWD_SINGLE_KERNEL).
+void set_single_kernel_backward(bool on) { g_bwd_flags = on ? FA_BWD_SINGLE_KERNEL : 0; }
+bool get_single_kernel_backward() { return (g_bwd_flags & FA_BWD_SINGLE_KERNEL) != 0; }
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -507,4 +518,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("combine_gather", &combine_gather, "Merge per-rank partial (O fp16, LSE) read in place, peer memory allowed");
   m.def("sum_gather", &sum_gather, "Sum per-rank partial dQ (fp16) read in place, peer memory allowed");
   m.def("device_status", &device_status, "Synchronise and read the device status word");
+  m.def("set_single_kernel_backward", &set_single_kernel_backward,
+        "Select the single-kernel backward (true) or the bitwise reproducible two-kernel backward (false, default)");
+  m.def("get_single_kernel_backward", &get_single_kernel_backward, "Which backward path is selected");
 }

@@ -102,9 +102,20 @@ int fa_fwd(const FaFwdParams* p, fa_stream_t stream);
 /* (flash_bwd_preprocess_kernel.h:23-96, flash_bwd_kernel.h:25-609 and :613-1344).  dK and dV    */
 /* are written per KV head; the per-query-head buffers and the torch::sum_out reduction of the   */
 /* reference (flash_api.cpp:338-348) do not exist here.                                          */
-/* Scratch: `workspace` must hold fa_bwd_workspace_bytes() bytes (fp32 rowsum(dO*O) and the LSE  */
-/* in base-2 units).                                                                             */
+/* Two paths, chosen by `flags`:                                                                 */
+/*   default (0)          a dQ kernel and a dK/dV kernel (seven products, like the reference's two  */
+/*                        kernels); every result is bitwise reproducible run to run;               */
+/*   FA_BWD_SINGLE_KERNEL ONE kernel with the five algorithmic products (S, dP, dV, dK, dQ); dQ is  */
+/*                        accumulated in an fp32 scratch buffer with global reductions whose order */
+/*                        depends on scheduling, so dQ is not bitwise reproducible (dK, dV are),  */
+/*                        then converted to fp16 by a small pass.  Fewer tensor-core operations,  */
+/*                        but the reductions cost the L2 cache more than the recomputation costs  */
+/*                        the tensor cores: measured slower on B200 at every benchmark shape.     */
+/* Scratch: `workspace` (256-byte aligned) must hold fa_bwd_workspace_bytes() bytes: fp32         */
+/* rowsum(dO*O) and the LSE in base-2 units, and for FA_BWD_SINGLE_KERNEL the fp32 dQ accumulator */
+/* (heads x padded rows x d).  The size depends on `flags`.                                      */
 /* ------------------------------------------------------------------------------------------- */
+#define FA_BWD_SINGLE_KERNEL 1
 typedef struct FaBwdParams {
   const void* q;
   const void* k;
@@ -132,14 +143,17 @@ typedef struct FaBwdParams {
   const int32_t* cu_seqlens_k;
   void* workspace;
   size_t workspace_bytes;
+  int32_t flags;      /* 0 or FA_BWD_SINGLE_KERNEL */
+  int32_t reserved0;
 } FaBwdParams;
 
 size_t fa_bwd_workspace_bytes(const FaBwdParams* p);
 int fa_bwd(const FaBwdParams* p, fa_stream_t stream);
 
-/* Runs a subset of the three kernels of fa_bwd(): stage_mask bit 0 = preprocess (rowsum(dO*O), LSE in
- * base-2 units -> workspace), bit 1 = dQ kernel, bit 2 = dK/dV kernel.  fa_bwd(p, s) is
- * fa_bwd_stages(p, 7, s).  For timing one kernel at a time with CUDA events around the call (the
+/* Runs a subset of the launches of fa_bwd(): stage_mask bit 0 = preprocess (rowsum(dO*O), LSE in
+ * base-2 units -> workspace; FA_BWD_SINGLE_KERNEL: also clears the dQ accumulator), bit 1 = the dQ kernel
+ * (FA_BWD_SINGLE_KERNEL: the single backward kernel), bit 2 = the dK/dV kernel (FA_BWD_SINGLE_KERNEL: the
+ * fp32 -> fp16 pass over dQ).  fa_bwd(p, s) is fa_bwd_stages(p, 7, s).  For timing one kernel at a time with CUDA events around the call (the
  * reference launches its three kernels back to back in run_flash_bwd,
  * src/flash_bwd_launch_template.h:84-138, and offers no such hook); bits 1 and 2 need a workspace that
  * an earlier call with bit 0 filled for the same inputs. */

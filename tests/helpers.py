@@ -194,9 +194,12 @@ def emulate_reference_kernel_varlen(q, k, v, dout, cu_q, cu_k, scale, causal) ->
 # 1.25 on tensors large enough to average over.
 # NOISE: where the expected result cancels to zero exactly (a single key: dS = P (dP - D) = 0) both kernels
 # return the fp32 accumulation noise of their tensor cores, which the torch emulation does not reproduce
-# (measured here: up to 2.0e-4 at the sizes of the grid, N(0,1) inputs).
+# (measured here: up to 2.0e-4 at the sizes of the grid, N(0,1) inputs).  It is granted only there, i.e. when
+# the largest expected value is below NOISE_WMAX; elsewhere the allowance is 1e-5 of the largest expected value.
 NOISE_ABS = 2.5e-4
+NOISE_WMAX = 1e-2
 MEAN_FACTOR, MEAN_FACTOR_SMALL, SMALL_NUMEL = 1.25, 2.0, 32768
+MEAN_FACTOR_TINY, TINY_NUMEL = 3.0, 4096  # e.g. a single query row: a few rounding events decide the mean as well
 # Every comparison is recorded; with FA_PARITY_LOG=<file> the session writes the records there (conftest.py),
 # and with FA_PARITY_SOFT=1 the bounds are recorded without being asserted (to survey a new kernel in one run).
 PARITY_LOG: list = []
@@ -216,8 +219,10 @@ def assert_within_twice_reference_kernel(name: str, got: torch.Tensor, want: tor
     wmax = w.abs().max().item()
     mx, rmx, mean, rmean = err.max().item(), ref.max().item(), err.mean().item(), ref.mean().item()
     granularity = getattr(emul, "one_event", 0.0) + half_ulp16(wmax)
-    max_bound = factor * rmx + granularity + NOISE_ABS
-    mean_bound = (MEAN_FACTOR if w.numel() >= SMALL_NUMEL else MEAN_FACTOR_SMALL) * rmean + NOISE_ABS / 4
+    noise = NOISE_ABS if wmax < NOISE_WMAX else 1e-5 * wmax
+    max_bound = factor * rmx + granularity + noise
+    mean_factor = MEAN_FACTOR if w.numel() >= SMALL_NUMEL else (MEAN_FACTOR_SMALL if w.numel() >= TINY_NUMEL else MEAN_FACTOR_TINY)
+    mean_bound = mean_factor * rmean + noise / 4
     PARITY_LOG.append(dict(name=name, err=mx, ref=rmx, mean=mean, refmean=rmean, wmax=wmax, numel=w.numel(),
                            max_bound=max_bound, mean_bound=mean_bound))
     if _SOFT:

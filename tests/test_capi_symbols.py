@@ -28,7 +28,7 @@ def test_every_declared_symbol_is_exported():
     lib = capi.lib()
     for name in _declared_functions():
         assert getattr(lib, name) is not None, name
-    assert lib.fa_abi_version() == 1
+    assert lib.fa_abi_version() == 2
 
 
 def test_struct_layouts_match_the_header(tmp_path):
@@ -37,13 +37,13 @@ def test_struct_layouts_match_the_header(tmp_path):
         '#include <stdio.h>\n#include <stddef.h>\n#include "fa_b200.h"\n'
         "int main(void){printf(\"%zu %zu %zu %zu %zu %zu %zu\\n\", sizeof(FaFwdParams), sizeof(FaBwdParams),"
         " sizeof(FaKvcacheParams), sizeof(FaCombineParams), offsetof(FaFwdParams, softmax_scale),"
-        " offsetof(FaBwdParams, workspace), offsetof(FaKvcacheParams, num_splits)); return 0;}\n")
+        " offsetof(FaBwdParams, flags), offsetof(FaKvcacheParams, num_splits)); return 0;}\n")
     exe = tmp_path / "sizes"
     subprocess.run(["gcc", "-std=c99", "-I", str(HEADER.parent), str(src), "-o", str(exe)], check=True)
     got = [int(x) for x in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
     want = [ctypes.sizeof(capi.FaFwdParams), ctypes.sizeof(capi.FaBwdParams), ctypes.sizeof(capi.FaKvcacheParams),
             ctypes.sizeof(capi.FaCombineParams), capi.FaFwdParams.softmax_scale.offset,
-            capi.FaBwdParams.workspace.offset, capi.FaKvcacheParams.num_splits.offset]
+            capi.FaBwdParams.flags.offset, capi.FaKvcacheParams.num_splits.offset]
     assert got == want
 
 
@@ -66,8 +66,10 @@ def test_host_side_argument_checks_need_no_gpu():
 def test_workspace_queries():
     lib = capi.lib()
     b = capi.FaBwdParams()
-    b.b, b.h, b.seqlen_q = 2, 4, 130
-    assert lib.fa_bwd_workspace_bytes(ctypes.byref(b)) == 2 * 2 * 4 * 256 * 4
+    b.b, b.h, b.seqlen_q, b.d = 2, 4, 130, 64
+    assert lib.fa_bwd_workspace_bytes(ctypes.byref(b)) == 2 * 2 * 4 * 256 * 4  # two fp32 statistics per padded row
+    b.flags = capi.FA_BWD_SINGLE_KERNEL  # plus the fp32 dQ accumulator (heads x padded rows x d)
+    assert lib.fa_bwd_workspace_bytes(ctypes.byref(b)) == 2 * 2 * 4 * 256 * 4 + 4 * (2 * 256) * 64 * 4
     k = capi.FaKvcacheParams()
     k.b, k.seqlen_q, k.h, k.h_k, k.d, k.cache_batch, k.seqlen_cache, k.num_splits = 2, 1, 8, 2, 128, 2, 4096, 4
     assert lib.fa_kvcache_num_splits(ctypes.byref(k)) == 4

@@ -35,11 +35,23 @@ def _check(name, got, want, emul, absolute=True):
         assert_reference_suite_bounds(name, got, want, emul)
 
 
+@pytest.fixture
+def single_kernel_backward(ext):
+    """Runs the test body with the single-kernel backward selected, and puts the default back afterwards."""
+    ext.set_single_kernel_backward(True)
+    yield
+    ext.set_single_kernel_backward(False)
+
+
+@pytest.mark.parametrize("path", ["single_kernel", "two_kernels"])
 @pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("sq,sk", SEQ_PAIRS)
-def test_dense_forward_backward_grid(ext, d, causal, sq, sk):
+def test_dense_forward_backward_grid(ext, request, d, causal, sq, sk, path):
     from flash_attention_turing_b200 import flash_attn_func
+
+    if path == "single_kernel":
+        request.getfixturevalue("single_kernel_backward")
 
     idx = SEQ_PAIRS.index((sq, sk))
     h, hk = HEAD_PAIRS[idx % len(HEAD_PAIRS)]
@@ -160,8 +172,12 @@ def _varlen_case(seed, lens_q, lens_k, h, hk, d):
     ([1, 2, 3, 129, 255], [7, 2, 300, 129, 1], 6, 3),
     ([640], [640], 4, 4),
 ])
-def test_varlen_forward_backward(ext, d, causal, lens_q, lens_k, h, hk):
+@pytest.mark.parametrize("path", ["single_kernel", "two_kernels"])
+def test_varlen_forward_backward(ext, request, d, causal, lens_q, lens_k, h, hk, path):
     from flash_attention_turing_b200 import flash_attn_varlen_func
+
+    if path == "single_kernel":
+        request.getfixturevalue("single_kernel_backward")
 
     q, k, v, dout, cq, ck = _varlen_case(31 + d, lens_q, lens_k, h, hk, d)
     qd, kd, vd = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
@@ -208,19 +224,48 @@ def test_varlen_packed_variants(ext):
 
 
 def test_run_to_run_determinism(ext):
-    # every accumulation order is fixed (no atomics): repeated launches are bit-identical, which also
-    # catches races on shared memory / TMEM
+    # Two-kernel backward (the default): every accumulation order is fixed (no atomics), so repeated launches are
+    # bit-identical, which also catches races on shared memory / TMEM.  Single-kernel backward: O, LSE, dK, dV
+    # are bit-identical as well; dQ is summed with global fp32 reductions in scheduling order, so it is only
+    # held to agree within one fp16 ulp of its largest value from run to run.
     q, k, v, dout = _inputs(77, 2, 700, 700, 4, 2, 128)
     qd, kd, vd, dd = (x.to(DEV) for x in (q, k, v, dout))
-    first = None
-    for _ in range(3):
-        out, lse = ext.fwd(qd, kd, vd, 128 ** -0.5, True)
-        grads = ext.bwd(qd, kd, vd, out, lse, dd, 128 ** -0.5, True)
-        cur = [out, lse, *grads]
-        if first is None:
-            first = [x.clone() for x in cur]
-        else:
-            assert all(torch.equal(a, b) for a, b in zip(first, cur))
+    for single in (False, True):
+        ext.set_single_kernel_backward(single)
+        try:
+            first = None
+            for _ in range(3):
+                out, lse = ext.fwd(qd, kd, vd, 128 ** -0.5, True)
+                dq, dk, dv = ext.bwd(qd, kd, vd, out, lse, dd, 128 ** -0.5, True)
+                cur = [out, lse, dk, dv, dq]
+                if first is None:
+                    first = [x.clone() for x in cur]
+                    continue
+                assert all(torch.equal(a, b) for a, b in zip(first[:4], cur[:4]))
+                if not single:
+                    assert torch.equal(first[4], dq)
+                else:
+                    ulp = 2.0 ** -10 * first[4].float().abs().max().item()
+                    assert (first[4].float() - dq.float()).abs().max().item() <= ulp
+        finally:
+            ext.set_single_kernel_backward(False)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_both_backward_paths_agree(ext, d):
+    # the single-kernel and the two-kernel backward compute the same sums with the same rounding points:
+    # dK and dV agree bit for bit or within an ulp (different accumulation chunks), dQ within an ulp
+    q, k, v, dout = _inputs(78, 2, 600, 900, 6, 2, d)
+    qd, kd, vd, dd = (x.to(DEV) for x in (q, k, v, dout))
+    out, lse = ext.fwd(qd, kd, vd, d ** -0.5, True)
+    a = ext.bwd(qd, kd, vd, out, lse, dd, d ** -0.5, True)
+    ext.set_single_kernel_backward(True)
+    try:
+        b = ext.bwd(qd, kd, vd, out, lse, dd, d ** -0.5, True)
+    finally:
+        ext.set_single_kernel_backward(False)
+    for x, y in zip(a, b):
+        assert (x.float() - y.float()).abs().max().item() <= 2.0 ** -9 * max(1.0, y.float().abs().max().item())
 
 
 def test_no_grad_and_requires_grad_flags(ext):
@@ -432,9 +477,10 @@ def _canaries_intact(buf, mask):
     return bool((raw[~mask] == want).all().item())
 
 
+@pytest.mark.parametrize("flags", [0, 1])  # 0: two-kernel backward, 1: FA_BWD_SINGLE_KERNEL
 @pytest.mark.parametrize("b,sq,sk,h,hk,d,causal", [(2, 129, 257, 4, 2, 64, True), (1, 385, 131, 3, 1, 128, False),
                                                    (2, 1, 300, 2, 2, 128, True), (1, 700, 700, 6, 3, 64, True)])
-def test_guard_bands_around_outputs_and_scratch(b, sq, sk, h, hk, d, causal):
+def test_guard_bands_around_outputs_and_scratch(b, sq, sk, h, hk, d, causal, flags):
     """Nothing is written outside the tensors the caller handed over: O, LSE, dQ, dK, dV and the backward
     scratch are cut out of canary-filled buffers (pads before and after, a gap after every row) through the
     C ABI's strides, and the canaries are intact after forward and backward at odd sizes.  (The memory
@@ -456,6 +502,7 @@ def test_guard_bands_around_outputs_and_scratch(b, sq, sk, h, hk, d, causal):
     scale = d ** -0.5
     capi.check(lib.fa_fwd(ctypes.byref(capi.fwd_params(q, k, v, o, lse, scale, causal)), stream))
     bp = capi.bwd_params(q, k, v, o, dout, lse, dq, dk, dv, None, scale, causal)
+    bp.flags = flags
     need = lib.fa_bwd_workspace_bytes(ctypes.byref(bp))
     ws_buf = torch.empty(need + 8192, dtype=torch.uint8, device=DEV)
     ws_buf.fill_(0xA5)
