@@ -43,7 +43,8 @@ class FaFwdParams(C.Structure):
            ("h_k", _i32), ("d", _i32), ("total_q", _i32), ("total_k", _i32), ("k_batch", _i32),
            ("softmax_scale", _f32), ("is_causal", _i32), ("cu_seqlens_q", _vp), ("cu_seqlens_k", _vp),
            ("seqused_k", _vp), ("cache_batch_idx", _vp), ("block_table", _vp),
-           ("block_table_batch_stride", _i64), ("page_size", _i32), ("block_table_cols", _i32)]
+           ("block_table_batch_stride", _i64), ("page_size", _i32), ("block_table_cols", _i32),
+           ("causal_shift", _i32), ("reserved0", _i32)]
     )
 
 
@@ -55,11 +56,12 @@ class FaBwdParams(C.Structure):
         + [("lse_row_stride", _i64), ("b", _i32), ("seqlen_q", _i32), ("seqlen_k", _i32), ("h", _i32),
            ("h_k", _i32), ("d", _i32), ("total_q", _i32), ("total_k", _i32), ("softmax_scale", _f32),
            ("is_causal", _i32), ("cu_seqlens_q", _vp), ("cu_seqlens_k", _vp), ("workspace", _vp),
-           ("workspace_bytes", _sz), ("flags", _i32), ("reserved0", _i32)]
+           ("workspace_bytes", _sz), ("flags", _i32), ("causal_shift", _i32)]
     )
 
 
 FA_BWD_SINGLE_KERNEL = 1
+FA_CAUSAL_SHIFT = 2
 
 
 class FaKvcacheParams(C.Structure):
@@ -90,7 +92,7 @@ class FaCombineGatherParams(C.Structure):
 
 class FaSumGatherParams(C.Structure):
     _fields_ = [("part", _vp * 16), ("out", _vp), ("num_parts", _i32), ("b", _i32), ("h", _i32), ("seqlen_q", _i32),
-                ("d", _i32), ("row_begin", _i32), ("rows", _i32), ("reserved0", _i32)]
+                ("d", _i32), ("row_begin", _i32), ("rows", _i32), ("reserved0", _i32), ("part_first_row", _i32 * 16)]
 
 
 class FaError(RuntimeError):

@@ -22,6 +22,7 @@ struct BwdKernelParams {
   int seqlen_q, seqlen_k, h, h_k;
   float scale, scale_log2;
   int is_causal;
+  int causal_shift;  // is_causal == 2: key j visible to query i iff j <= i + causal_shift (else sk - sq is used)
   const int* cu_seqlens_q;
   const int* cu_seqlens_k;
   int* status;

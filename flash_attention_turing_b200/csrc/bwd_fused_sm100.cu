@@ -110,8 +110,9 @@ bwd_fused_kernel(const __grid_constant__ BwdKernelParams p) {
   const int group = p.h / p.h_k;
   const int nq = (sq + kBlock - 1) / kBlock;
   int i_min = 0;
+  const int shift = (p.is_causal == 2) ? p.causal_shift : sk - sq;  // key j visible to query i iff j <= i + shift
   if (p.is_causal) {
-    const int first_row = key0 - (sk - sq);  // first query row that can see key0
+    const int first_row = key0 - shift;  // first query row that can see key0
     i_min = first_row <= 0 ? 0 : first_row / kBlock;
   }
   const int per_head = max(0, nq - i_min);
@@ -225,7 +226,7 @@ bwd_fused_kernel(const __grid_constant__ BwdKernelParams p) {
     const int sw = row_in_tile & 7;
     const float c = p.scale_log2;
     const float2 c2 = make_float2(c, c);
-    const int cmin0 = p.is_causal ? key - (sk - sq) - (i_min * kBlock + cq * 32) : 0;
+    const int cmin0 = p.is_causal ? key - shift - (i_min * kBlock + cq * 32) : 0;
     const float* stats = sStats + cq * 32;
     const int cmax_last = fix_q_tail ? max(0, min(32, q_tail_rows - cq * 32)) : 32;  // valid columns in the last Q tile
     int i_rel = 0;  // Q tile within the current head

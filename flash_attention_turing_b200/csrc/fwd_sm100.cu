@@ -52,6 +52,7 @@ struct FwdKernelParams {
   float scale;       // softmax scale
   float scale_log2;  // softmax scale * log2(e)
   int is_causal;
+  int causal_shift;   // is_causal == 2: key j visible to query i iff j <= i + causal_shift (else sk - sq is used)
   const int* cu_seqlens_q;
   const int* cu_seqlens_k;
   const int* seqused_k;
@@ -121,6 +122,8 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
   const int bk = varlen_k ? 0 : (p.cache_batch_idx ? p.cache_batch_idx[batch] : batch);
   const int head_k = head / (p.h / p.h_k);
 
+  // causal diagonal: key j is visible to query i iff j <= i + shift
+  const int shift = (p.is_causal == 2) ? p.causal_shift : sk - sq;
   // number of K/V blocks each tile visits
   const int nkb = (sk + kBlockN - 1) / kBlockN;
   int nb[kTiles];
@@ -129,7 +132,7 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
     const int r0 = row0 + t * kBlockM;
     int n = nkb;
     if (p.is_causal) {
-      const int x = r0 + kBlockM + sk - sq;  // one past the last visible key of the tile's last row
+      const int x = r0 + kBlockM + shift;  // one past the last visible key of the tile's last row
       n = x <= 0 ? 0 : min(nkb, (x + kBlockN - 1) / kBlockN);
     }
     if (r0 >= sq) n = 0;
@@ -379,7 +382,7 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
       // masking: only blocks that touch the sequence end or the causal diagonal
       const int col0 = j * kBlockN;
       int lim = sk - 1 - col0;  // last visible column index within this block
-      if (p.is_causal) lim = min(lim, row + sk - sq - col0);
+      if (p.is_causal) lim = min(lim, row + shift - col0);
       const bool masked = lim < kBlockN - 1;
       auto mask32 = [&](uint32_t (&v)[32], int base) {
         if (masked) {
@@ -571,6 +574,9 @@ int run_fwd(const FaFwdParams* p, int seqused_k_add, cudaStream_t stream) {
                    (p->cu_seqlens_q || p->o_batch_stride % 8 == 0),
                "fa_fwd: o must be 16-byte aligned with strides that are multiples of 8 elements");
   FA_CHECK_ARG(p->lse_row_stride >= p->seqlen_q, "fa_fwd: lse_row_stride is smaller than seqlen_q");
+  FA_CHECK_ARG(p->is_causal >= 0 && p->is_causal <= 2, "fa_fwd: is_causal must be 0, 1 or FA_CAUSAL_SHIFT");
+  FA_CHECK_ARG(p->is_causal != 2 || (!p->cu_seqlens_q && !p->seqused_k && !p->block_table),
+               "fa_fwd: FA_CAUSAL_SHIFT is for dense q / k / v only");
   if (p->block_table) {
     FA_CHECK_ARG(p->page_size >= 128 && p->page_size % 128 == 0,
                  "fa_fwd: page_size must be a positive multiple of 128");
@@ -622,6 +628,7 @@ int run_fwd(const FaFwdParams* p, int seqused_k_add, cudaStream_t stream) {
   kp.scale = p->softmax_scale;
   kp.scale_log2 = p->softmax_scale * kLog2e;
   kp.is_causal = p->is_causal;
+  kp.causal_shift = p->causal_shift;
   kp.cu_seqlens_q = p->cu_seqlens_q;
   kp.cu_seqlens_k = p->cu_seqlens_k;
   kp.seqused_k = p->seqused_k;

@@ -33,9 +33,24 @@ void check_half_cuda(const at::Tensor& t, const char* name) {
 
 fa_stream_t current_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 
+// A log-sum-exp tensor (b, h, rows) given by the caller: fp32, unit stride along rows, heads of a batch one
+// row pitch apart -- e.g. a slice of the rows of a contiguous tensor.
+void check_lse_view(const at::Tensor& l, int64_t b, int64_t h, int64_t rows, const char* name) {
+  TORCH_CHECK(l.is_cuda() && l.scalar_type() == torch::kFloat32 && l.dim() == 3, name,
+              " must be a float32 CUDA tensor of rank 3");
+  TORCH_CHECK(l.size(0) == b && l.size(1) == h && l.size(2) == rows, name,
+              " must have shape [batch_size, nheads_q, seqlen_q]");
+  TORCH_CHECK((rows == 1 || l.stride(2) == 1) && l.stride(1) >= rows && (b == 1 || l.stride(0) == h * l.stride(1)), name,
+              " must have unit stride along the rows and batches h row pitches apart");
+}
+
 // ---- dense forward (mha_fwd, flash_api.cpp:188-256) ----
+// out_, lse_ (optional, after the reference's five arguments): write O and LSE there instead of into new tensors
+// (strided views are fine: e.g. a block of rows of a larger buffer).  causal_shift_ (optional): with is_causal,
+// key j is visible to query i iff j <= i + causal_shift instead of the bottom-right alignment.
 std::vector<at::Tensor> mha_fwd(at::Tensor q, at::Tensor k, at::Tensor v, const double softmax_scale,
-                                bool is_causal) {
+                                bool is_causal, c10::optional<at::Tensor> out_, c10::optional<at::Tensor> lse_,
+                                c10::optional<int64_t> causal_shift_) {
   TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "q, k, v must be rank-4 tensors");
   check_half_cuda(q, "q");
   check_half_cuda(k, "k");
@@ -50,8 +65,14 @@ std::vector<at::Tensor> mha_fwd(at::Tensor q, at::Tensor k, at::Tensor v, const 
   check_supported_head_dim(head_size);
   c10::cuda::CUDAGuard guard(q.device());
 
-  at::Tensor o = torch::empty(q.sizes(), q.options());
-  at::Tensor l = torch::empty({batch_size, num_heads, seqlen_q}, q.options().dtype(torch::kFloat32));
+  at::Tensor o = (out_.has_value() && out_->defined()) ? *out_ : torch::empty(q.sizes(), q.options());
+  at::Tensor l = (lse_.has_value() && lse_->defined())
+                     ? *lse_ : torch::empty({batch_size, num_heads, seqlen_q}, q.options().dtype(torch::kFloat32));
+  if (out_.has_value() && out_->defined()) {
+    check_half_cuda(o, "out");
+    TORCH_CHECK(o.sizes() == q.sizes() && o.device() == q.device(), "out must have the shape and device of q");
+  }
+  if (lse_.has_value() && lse_->defined()) check_lse_view(l, batch_size, num_heads, seqlen_q, "lse");
   if (batch_size == 0 || seqlen_q == 0) return {o, l};
   if (seqlen_k == 0) {
     o.zero_();
@@ -66,12 +87,16 @@ std::vector<at::Tensor> mha_fwd(at::Tensor q, at::Tensor k, at::Tensor v, const 
   p.k_batch_stride = k.stride(0); p.k_row_stride = k.stride(1); p.k_head_stride = k.stride(2);
   p.v_batch_stride = v.stride(0); p.v_row_stride = v.stride(1); p.v_head_stride = v.stride(2);
   p.o_batch_stride = o.stride(0); p.o_row_stride = o.stride(1); p.o_head_stride = o.stride(2);
-  p.lse_row_stride = seqlen_q;
+  p.lse_row_stride = l.stride(1);
   p.b = batch_size; p.seqlen_q = seqlen_q; p.seqlen_k = seqlen_k;
   p.h = num_heads; p.h_k = num_heads_k; p.d = head_size;
   p.k_batch = batch_size;
   p.softmax_scale = static_cast<float>(softmax_scale);
   p.is_causal = is_causal;
+  if (is_causal && causal_shift_.has_value()) {
+    p.is_causal = FA_CAUSAL_SHIFT;
+    p.causal_shift = static_cast<int32_t>(*causal_shift_);
+  }
   check_rc(fa_fwd(&p, current_stream()), "fa_fwd");
   return {o, l};
 }
@@ -157,7 +182,7 @@ at::Tensor grad_destination(const c10::optional<at::Tensor>& given, const at::Te
 std::vector<at::Tensor> mha_bwd(at::Tensor q, at::Tensor k, at::Tensor v, at::Tensor out, at::Tensor l,
                                 at::Tensor dout, const double softmax_scale, bool is_causal,
                                 c10::optional<at::Tensor> dq_, c10::optional<at::Tensor> dk_,
-                                c10::optional<at::Tensor> dv_) {
+                                c10::optional<at::Tensor> dv_, c10::optional<int64_t> causal_shift_) {
   TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "q, k, v must be rank-4 tensors");
   TORCH_CHECK(out.dim() == 4 && dout.dim() == 4, "out and dout must be rank-4 tensors");
   check_half_cuda(q, "q"); check_half_cuda(k, "k"); check_half_cuda(v, "v");
@@ -171,10 +196,7 @@ std::vector<at::Tensor> mha_bwd(at::Tensor q, at::Tensor k, at::Tensor v, at::Te
   TORCH_CHECK(out.sizes() == q.sizes() && dout.sizes() == q.sizes(), "out and dout must match q shape");
   TORCH_CHECK(num_heads % num_heads_k == 0, "num_heads_q must be divisible by num_heads_k for GQA/MQA");
   check_supported_head_dim(head_size);
-  TORCH_CHECK(l.is_cuda() && l.scalar_type() == torch::kFloat32 && l.dim() == 3 && l.is_contiguous(),
-              "l must be a contiguous float32 CUDA tensor of rank 3");
-  TORCH_CHECK(l.size(0) == batch_size && l.size(1) == num_heads && l.size(2) == seqlen_q,
-              "l must have shape [batch_size, nheads_q, seqlen_q]");
+  check_lse_view(l, batch_size, num_heads, seqlen_q, "l");
   c10::cuda::CUDAGuard guard(q.device());
 
   at::Tensor dq = grad_destination(dq_, q, "dq", false);
@@ -197,11 +219,15 @@ std::vector<at::Tensor> mha_bwd(at::Tensor q, at::Tensor k, at::Tensor v, at::Te
   p.dq_batch_stride = dq.stride(0); p.dq_row_stride = dq.stride(1); p.dq_head_stride = dq.stride(2);
   p.dk_batch_stride = dk.stride(0); p.dk_row_stride = dk.stride(1); p.dk_head_stride = dk.stride(2);
   p.dv_batch_stride = dv.stride(0); p.dv_row_stride = dv.stride(1); p.dv_head_stride = dv.stride(2);
-  p.lse_row_stride = seqlen_q;
+  p.lse_row_stride = l.stride(1);
   p.b = batch_size; p.seqlen_q = seqlen_q; p.seqlen_k = seqlen_k;
   p.h = num_heads; p.h_k = num_heads_k; p.d = head_size;
   p.softmax_scale = static_cast<float>(softmax_scale);
   p.is_causal = is_causal;
+  if (is_causal && causal_shift_.has_value()) {
+    p.is_causal = FA_CAUSAL_SHIFT;
+    p.causal_shift = static_cast<int32_t>(*causal_shift_);
+  }
   p.flags = g_bwd_flags;
   const size_t ws = fa_bwd_workspace_bytes(&p);
   at::Tensor workspace = torch::empty({static_cast<int64_t>(ws)}, q.options().dtype(torch::kUInt8));
@@ -469,7 +495,9 @@ std::vector<at::Tensor> combine_gather(std::vector<at::Tensor> o_parts, std::vec
 }
 
 // ---- sum of per-rank partial dQ read in place (parts[r] may be peer-mapped memory of another GPU) ----
-at::Tensor sum_gather(std::vector<at::Tensor> parts, int64_t row_begin, int64_t rows) {
+// first_rows (optional): per part, the first query row that holds anything (rows below are not read).
+at::Tensor sum_gather(std::vector<at::Tensor> parts, int64_t row_begin, int64_t rows,
+                      c10::optional<std::vector<int64_t>> first_rows) {
   TORCH_CHECK(!parts.empty() && parts.size() <= FA_MAX_GATHER_PARTS, "between 1 and ", FA_MAX_GATHER_PARTS, " parts");
   const at::Tensor& p0 = parts[0];
   TORCH_CHECK(p0.dim() == 4, "partial dQ must be (b, seqlen_q, h, d)");
@@ -481,6 +509,10 @@ at::Tensor sum_gather(std::vector<at::Tensor> parts, int64_t row_begin, int64_t 
                     parts[i].sizes() == p0.sizes(),
                 "partial dQ tensors must be contiguous float16 CUDA tensors of one shape");
     p.part[i] = parts[i].data_ptr();
+  }
+  if (first_rows.has_value()) {
+    TORCH_CHECK(first_rows->size() == parts.size(), "first_rows must have one entry per part");
+    for (size_t i = 0; i < parts.size(); ++i) p.part_first_row[i] = static_cast<int32_t>((*first_rows)[i]);
   }
   TORCH_CHECK(row_begin >= 0 && rows >= 0 && row_begin + rows <= s, "row range out of bounds");
   auto opts = at::TensorOptions().device(at::kCUDA, at::cuda::current_device());
@@ -504,10 +536,12 @@ bool get_single_kernel_backward() { return (g_bwd_flags & FA_BWD_SINGLE_KERNEL) 
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.def("fwd", &mha_fwd, "Forward pass");
+  m.def("fwd", &mha_fwd, "Forward pass", py::arg("q"), py::arg("k"), py::arg("v"), py::arg("softmax_scale"),
+        py::arg("is_causal"), py::arg("out") = py::none(), py::arg("lse") = py::none(),
+        py::arg("causal_shift") = py::none());
   m.def("bwd", &mha_bwd, "Backward pass", py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("l"),
         py::arg("dout"), py::arg("softmax_scale"), py::arg("is_causal"), py::arg("dq") = py::none(),
-        py::arg("dk") = py::none(), py::arg("dv") = py::none());
+        py::arg("dk") = py::none(), py::arg("dv") = py::none(), py::arg("causal_shift") = py::none());
   m.def("varlen_fwd", &mha_varlen_fwd, "Varlen forward pass");
   m.def("varlen_bwd", &mha_varlen_bwd, "Varlen backward pass", py::arg("q"), py::arg("k"), py::arg("v"),
         py::arg("out"), py::arg("l"), py::arg("dout"), py::arg("cu_seqlens_q"), py::arg("cu_seqlens_k"),
@@ -516,7 +550,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fwd_kvcache", &mha_fwd_kvcache, "KV-cache forward pass");
   m.def("combine", &combine, "Merge split partials (O fp32, LSE) with log-sum-exp weights");
   m.def("combine_gather", &combine_gather, "Merge per-rank partial (O fp16, LSE) read in place, peer memory allowed");
-  m.def("sum_gather", &sum_gather, "Sum per-rank partial dQ (fp16) read in place, peer memory allowed");
+  m.def("sum_gather", &sum_gather, "Sum per-rank partial dQ (fp16) read in place, peer memory allowed", py::arg("parts"),
+        py::arg("row_begin"), py::arg("rows"), py::arg("first_rows") = py::none());
   m.def("device_status", &device_status, "Synchronise and read the device status word");
   m.def("set_single_kernel_backward", &set_single_kernel_backward,
         "Select the single-kernel backward (true) or the bitwise reproducible two-kernel backward (false, default)");

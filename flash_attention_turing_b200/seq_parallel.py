@@ -27,6 +27,12 @@ The ``*_p2p`` variants replace the collective by ONE kernel that reads the peers
 ``partial_attention`` and ``merge_partials`` take the kernels as injectable callables so that the
 exchange logic can be exercised by CPU ranks in the tests (with the oracle as the kernel stand-in);
 by default they call the CUDA library and fail if it is missing.
+
+On CUDA tensors with the default kernels the public functions take a path without eager tensor arithmetic:
+ONE forward (backward) launch per K/V chunk with an explicit causal diagonal (``causal_shift``), writing
+straight into row blocks of the exchange buffers; query rows a chunk cannot see are marked by LSE = -inf
+(forward) or by a per-part first valid row (backward) and are never read by the merge kernels; for one
+sequence (batch 1) the all-to-all sends the partial as it lies in memory.
 """
 from __future__ import annotations
 
@@ -144,17 +150,102 @@ def partial_attention(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Ten
     return out, lse
 
 
+def _fast(q: torch.Tensor, *injected) -> bool:
+    """The copy-free CUDA path applies when no stand-in kernel was injected."""
+    return q.is_cuda and all(x is None for x in injected)
+
+
+def chunk_first_rows(world: int, seqlen: int, layout: str, causal: bool):
+    """For every (rank, chunk) in the order the parts are merged: the first query row that sees a key of the
+    chunk (0 without a causal mask)."""
+    rows = []
+    for r in range(world):
+        for kb, _ in shard_chunks(r, world, seqlen, layout):
+            rows.append(min(kb, seqlen) if causal else 0)
+    return rows
+
+
+def rank_partials_inplace(q, k_shard, v_shard, rank: int, world: int, softmax_scale: float, causal: bool,
+                          layout: str, out_bufs: torch.Tensor, lse_bufs: torch.Tensor) -> None:
+    """One forward launch per chunk of this rank, written in place: out_bufs (chunks, b, s, h, d) and lse_bufs
+    (chunks, b, h, s).  Chunk c attends query rows [first, s) -- the rows that can see it -- against its keys
+    with the diagonal at key 0 <-> row `first` (causal_shift = 0); rows below `first` get LSE = -inf and their
+    O rows are left untouched (the merge kernels do not read them)."""
+    from . import _ext
+
+    ext = _ext.load()
+    s = q.shape[1]
+    local = 0
+    for ci, (kb, ke) in enumerate(shard_chunks(rank, world, s, layout)):
+        c = ke - kb
+        ks, vs = k_shard[:, local:local + c], v_shard[:, local:local + c]
+        local += c
+        first = min(kb, s) if causal else 0
+        if first > 0:
+            lse_bufs[ci][:, :, :first].fill_(float("-inf"))
+        if first < s:
+            ext.fwd(q[:, first:], ks, vs, softmax_scale, causal, out=out_bufs[ci][:, first:],
+                    lse=lse_bufs[ci][:, :, first:], causal_shift=0 if causal else None)
+
+
+def rank_backward_inplace(q, k_shard, v_shard, out, lse, dout, rank: int, world: int, softmax_scale: float,
+                          causal: bool, layout: str, dq_bufs: torch.Tensor, dk_shard: torch.Tensor,
+                          dv_shard: torch.Tensor) -> None:
+    """One backward launch per chunk of this rank: the chunk's dQ share goes to rows [first, s) of dq_bufs[c]
+    (chunks, b, s, h, d) -- rows below `first` are left untouched, the reduction skips them -- and its dK, dV
+    to the chunk's rows of dk_shard / dv_shard."""
+    from . import _ext
+
+    ext = _ext.load()
+    s = q.shape[1]
+    local = 0
+    for ci, (kb, ke) in enumerate(shard_chunks(rank, world, s, layout)):
+        c = ke - kb
+        first = min(kb, s) if causal else 0
+        sl = slice(local, local + c)
+        local += c
+        if first >= s:
+            dk_shard[:, sl].zero_()
+            dv_shard[:, sl].zero_()
+            continue
+        ext.bwd(q[:, first:], k_shard[:, sl], v_shard[:, sl], out[:, first:], lse[:, :, first:], dout[:, first:],
+                softmax_scale, causal, dq=dq_bufs[ci][:, first:], dk=dk_shard[:, sl], dv=dv_shard[:, sl],
+                causal_shift=0 if causal else None)
+
+
+def _exchange_rows(x: torch.Tensor, world: int, group) -> torch.Tensor:
+    """all_to_all of the query-row slices of x (b, s, h, d): returns (world, b, s / world, h, d), entry r = this
+    rank's slice as rank r holds it.  For one sequence the slices are sent as they lie in memory."""
+    b, s, h, d = x.shape
+    sl = s // world
+    send = x.view(world, 1, sl, h, d) if b == 1 else x.view(b, world, sl, h, d).transpose(0, 1).contiguous()
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    return recv
+
+
 def merge_partials(o_part: torch.Tensor, lse_part: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
                    combine: Optional[CombineFn] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Exchange and merge.  o_part (b, s, h, d), lse_part (b, h, s) are this rank's partials for ALL query
     rows; s must be divisible by the world size.  Returns this rank's slice of the final result:
     out (b, s / world, h, d) in o_part's dtype and lse (b, h, s / world) fp32."""
-    combine = combine or _default_combine
     world = dist.get_world_size(group)
     b, s, h, d = o_part.shape
     if s % world != 0:
         raise ValueError("seqlen_q must be divisible by the number of ranks")
     sl = s // world
+    if _fast(o_part, combine):
+        # the received slices are fp16 partials in the forward's own layout: fa_combine_gather merges them as
+        # they are (no conversion, no transposition of O); only the small LSE tensor is re-laid
+        from . import _ext
+
+        o_recv = _exchange_rows(o_part, world, group)
+        l_send = lse_part.view(b, h, world, sl).permute(2, 0, 1, 3).contiguous()
+        l_recv = torch.empty_like(l_send)
+        dist.all_to_all_single(l_recv, l_send, group=group)
+        out, lse = _ext.load().combine_gather(list(o_recv.unbind(0)), list(l_recv.unbind(0)), 0, sl)
+        return out, lse
+    combine = combine or _default_combine
     # send buffers: slice j of the query rows, laid out (b, h, sl, d) so that the received block of every
     # source rank is already in the (rows = (b, h, sl), d) order the combine kernel reads
     o_send = o_part.view(b, world, sl, h, d).permute(1, 0, 3, 2, 4).contiguous()      # (world, b, h, sl, d)
@@ -202,7 +293,20 @@ def sequence_parallel_forward(q: torch.Tensor, k_shard: torch.Tensor, v_shard: t
     rank = dist.get_rank(group)
     world = dist.get_world_size(group)
     scale = q.shape[-1] ** -0.5 if softmax_scale is None else softmax_scale
-    o_part, lse_part = rank_partial(q, k_shard, v_shard, rank, world, scale, causal, layout, fwd, merge2)
+    if _fast(q, fwd, combine, merge2):
+        b, s, h, d = q.shape
+        nch = 2 if _check_layout(layout) else 1
+        o_bufs = torch.empty((nch, b, s, h, d), dtype=q.dtype, device=q.device)
+        l_bufs = torch.empty((nch, b, h, s), dtype=torch.float32, device=q.device)
+        rank_partials_inplace(q, k_shard, v_shard, rank, world, scale, causal, layout, o_bufs, l_bufs)
+        if nch == 2:  # the two zig-zag chunks are merged locally, so that one partial travels
+            o_part, lse_part = _default_merge2(list(o_bufs.unbind(0)), list(l_bufs.unbind(0)))
+            dead = torch.isinf(l_bufs[0]) & torch.isinf(l_bufs[1])
+            lse_part = torch.where(dead, torch.full_like(lse_part, float("-inf")), lse_part)
+        else:
+            o_part, lse_part = o_bufs[0], l_bufs[0]
+    else:
+        o_part, lse_part = rank_partial(q, k_shard, v_shard, rank, world, scale, causal, layout, fwd, merge2)
     out, lse = merge_partials(o_part, lse_part, group, combine)
     if not gather_output:
         return out, lse
@@ -260,6 +364,14 @@ def peer_memory_available(shape_o, shape_l, dtype, device, group: Optional[dist.
     return bool(flag.item())
 
 
+def peer_memory_available_for(q: torch.Tensor, layout: str = "contiguous",
+                              group: Optional[dist.ProcessGroup] = None) -> bool:
+    """Collective.  ``peer_memory_available`` for the buffers the ``*_p2p`` functions use with this q and layout."""
+    b, s, h, d = q.shape
+    nch = 2 if _check_layout(layout) else 1
+    return peer_memory_available((nch, b, s, h, d), (nch, b, h, s), q.dtype, q.device, group)
+
+
 _last_p2p_error = [""]
 
 
@@ -288,10 +400,16 @@ def sequence_parallel_forward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_shar
     # Everything that can fail on the host -- allocation, rendezvous, mapping the peers' buffers, the local
     # kernels' argument checks -- happens before the first device-side barrier; between the two barriers the
     # merge runs under try/finally, so a rank that fails there still releases its peers.
-    o_buf, l_buf, hdl_o, hdl_l = _p2p_buffers(q.shape, (b, h, s), q.dtype, q.device, group)
-    o_parts = [hdl_o.get_buffer(r, q.shape, q.dtype) for r in range(world)]
-    l_parts = [hdl_l.get_buffer(r, (b, h, s), torch.float32) for r in range(world)]
-    rank_partial(q, k_shard, v_shard, rank, world, scale, causal, layout, None, None, o_buf, l_buf)
+    nch = 2 if _check_layout(layout) else 1
+    if nch * world > 16:
+        raise ValueError("at most 16 K/V chunks in total (8 ranks with the zigzag layout)")
+    shape_o, shape_l = (nch, b, s, h, d), (nch, b, h, s)
+    o_buf, l_buf, hdl_o, hdl_l = _p2p_buffers(shape_o, shape_l, q.dtype, q.device, group)
+    o_parts = [x for r in range(world) for x in hdl_o.get_buffer(r, shape_o, q.dtype).unbind(0)]
+    l_parts = [x for r in range(world) for x in hdl_l.get_buffer(r, shape_l, torch.float32).unbind(0)]
+    # one launch per chunk, written straight into the symmetric buffers; each chunk of each rank is one part of
+    # the merge (no local pre-merge of the two zig-zag chunks), dead rows are skipped through LSE = -inf
+    rank_partials_inplace(q, k_shard, v_shard, rank, world, scale, causal, layout, o_buf, l_buf)
     sl = s // world
     hdl_o.barrier(channel=0)  # every rank's partial is complete and visible
     try:
@@ -398,6 +516,26 @@ def sequence_parallel_backward(q: torch.Tensor, k_shard: torch.Tensor, v_shard: 
     rank = dist.get_rank(group)
     world = dist.get_world_size(group)
     scale = q.shape[-1] ** -0.5 if softmax_scale is None else softmax_scale
+    if _fast(q, bwd, sum_parts, add2):
+        from . import _ext
+
+        ext = _ext.load()
+        b, s, h, d = q.shape
+        if s % world != 0:
+            raise ValueError("seqlen_q must be divisible by the number of ranks")
+        sl = s // world
+        nch = 2 if _check_layout(layout) else 1
+        dq_bufs = torch.empty((nch, b, s, h, d), dtype=q.dtype, device=q.device)
+        dk, dv = torch.empty_like(k_shard), torch.empty_like(v_shard)
+        rank_backward_inplace(q, k_shard, v_shard, out, lse, dout, rank, world, scale, causal, layout, dq_bufs, dk, dv)
+        firsts = chunk_first_rows(world, s, layout, causal)
+        mine = firsts[rank * nch:(rank + 1) * nch]
+        # the two zig-zag shares are added locally (rows neither chunk sees come out as zero), then ONE share travels
+        share = ext.sum_gather(list(dq_bufs.unbind(0)), 0, s, mine) if nch == 2 else dq_bufs[0]
+        recv = _exchange_rows(share, world, group)  # (world, b, sl, h, d)
+        # rank r's share is valid from the first row its lowest chunk sees, here in the coordinates of this slice
+        first_in_slice = [max(0, min(sl, min(firsts[r * nch:(r + 1) * nch]) - rank * sl)) for r in range(world)]
+        return ext.sum_gather(list(recv.unbind(0)), 0, sl, first_in_slice), dk, dv
     dq_share, dk, dv = rank_backward(q, k_shard, v_shard, out, lse, dout, rank, world, scale, causal, layout, bwd,
                                      add2)
     return reduce_dq_shares(dq_share, group, sum_parts), dk, dv
@@ -420,13 +558,20 @@ def sequence_parallel_backward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_sha
     if s % world != 0:
         raise ValueError("seqlen_q must be divisible by the number of ranks")
     scale = d ** -0.5 if softmax_scale is None else softmax_scale
-    buf, _, hdl, _ = _p2p_buffers(q.shape, (b, h, s), q.dtype, q.device, group)
-    parts = [hdl.get_buffer(r, q.shape, q.dtype) for r in range(world)]
-    _, dk, dv = rank_backward(q, k_shard, v_shard, out, lse, dout, rank, world, scale, causal, layout, None, None, buf)
+    nch = 2 if _check_layout(layout) else 1
+    if nch * world > 16:
+        raise ValueError("at most 16 K/V chunks in total (8 ranks with the zigzag layout)")
+    shape_o, shape_l = (nch, b, s, h, d), (nch, b, h, s)
+    buf, _, hdl, _ = _p2p_buffers(shape_o, shape_l, q.dtype, q.device, group)
+    parts = [x for r in range(world) for x in hdl.get_buffer(r, shape_o, q.dtype).unbind(0)]
+    dk, dv = torch.empty_like(k_shard), torch.empty_like(v_shard)
+    # one launch per chunk; the dQ share of every chunk of every rank is one part of the sum, valid from the
+    # first row that sees the chunk (rows below are neither written here nor read over NVLink there)
+    rank_backward_inplace(q, k_shard, v_shard, out, lse, dout, rank, world, scale, causal, layout, buf, dk, dv)
     sl = s // world
     hdl.barrier(channel=0)  # every rank's share is complete and visible
     try:
-        dq = ext.sum_gather(parts, rank * sl, sl)
+        dq = ext.sum_gather(parts, rank * sl, sl, chunk_first_rows(world, s, layout, causal))
     finally:
         hdl.barrier(channel=1)  # nobody overwrites a share that a peer is still reading
     return dq, dk, dv

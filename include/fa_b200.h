@@ -12,8 +12,11 @@
  *
  * Tensor conventions: fp16 (IEEE half) data, fp32 log-sum-exp, int32 index arrays, all in device
  * memory.  Strides are in ELEMENTS and 64-bit; the innermost (head_dim) stride is always 1.
- * head_dim is 64 or 128.  Causal masking is bottom-right aligned: key j is visible to query i iff
- * j <= i + seqlen_k - seqlen_q.  A query row without a visible key gets O = 0 and LSE = 0.
+ * head_dim is 64 or 128.  Causal masking (is_causal = 1) is bottom-right aligned: key j is visible to query i
+ * iff j <= i + seqlen_k - seqlen_q.  With is_causal = FA_CAUSAL_SHIFT (2) the diagonal is placed by the caller:
+ * key j is visible to query i iff j <= i + causal_shift (dense layouts only) -- what a sequence-sharded run
+ * needs to attend a block of query rows against a K/V shard in one launch.  A query row without a visible
+ * key gets O = 0 and LSE = 0.
  */
 #ifndef FA_B200_H_
 #define FA_B200_H_
@@ -27,6 +30,8 @@ extern "C" {
 
 /* Same underlying type as cudaStream_t (struct CUstream_st*); void* keeps the header CUDA-free. */
 typedef void* fa_stream_t;
+
+#define FA_CAUSAL_SHIFT 2 /* value of is_causal: the causal diagonal is given by causal_shift */
 
 enum {
   FA_OK = 0,
@@ -91,6 +96,8 @@ typedef struct FaFwdParams {
   int64_t block_table_batch_stride;
   int32_t page_size;           /* tokens per page (multiple of 128) when block_table != NULL    */
   int32_t block_table_cols;    /* columns of block_table (0 = unknown: seqused_k is trusted)    */
+  int32_t causal_shift;        /* used when is_causal == FA_CAUSAL_SHIFT                        */
+  int32_t reserved0;
 } FaFwdParams;
 
 int fa_fwd(const FaFwdParams* p, fa_stream_t stream);
@@ -144,7 +151,7 @@ typedef struct FaBwdParams {
   void* workspace;
   size_t workspace_bytes;
   int32_t flags;      /* 0 or FA_BWD_SINGLE_KERNEL */
-  int32_t reserved0;
+  int32_t causal_shift; /* used when is_causal == FA_CAUSAL_SHIFT */
 } FaBwdParams;
 
 size_t fa_bwd_workspace_bytes(const FaBwdParams* p);
@@ -290,6 +297,9 @@ typedef struct FaSumGatherParams {
   int32_t num_parts, b, h, seqlen_q, d;
   int32_t row_begin, rows;
   int32_t reserved0;
+  /* part_first_row[r]: query rows below this index hold nothing in part r (a causal shard sees no key    */
+  /* there) and are neither read nor added; 0 = every row is valid.                                      */
+  int32_t part_first_row[FA_MAX_GATHER_PARTS];
 } FaSumGatherParams;
 
 int fa_sum_gather(const FaSumGatherParams* p, fa_stream_t stream);

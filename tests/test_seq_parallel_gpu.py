@@ -52,7 +52,7 @@ def _worker(rank, world, port, causal, d, results):
         # symmetric memory can be used is agreed on by all ranks on the host BEFORE anyone enters a device-side
         # barrier, so that no rank waits for a peer that gave up
         p2p_err = -1.0
-        if sp.peer_memory_available(qd.shape, (b, h, s), qd.dtype, dev):
+        if sp.peer_memory_available_for(qd):
             out_p, lse_p = sp.sequence_parallel_forward_p2p(qd, ks, vs, None, causal)
             torch.cuda.synchronize()
             sl = s // world
@@ -111,7 +111,11 @@ def _bwd_worker(rank, world, port, causal, d, results, layout="contiguous"):
         dq, dk, dv = sp.sequence_parallel_backward(qd, ks, vs, out, lse, dod, None, causal, layout=layout)
         torch.cuda.synchronize()
         p2p_err = -1.0
-        if sp.peer_memory_available(qd.shape, (b, h, s), qd.dtype, dev):
+        if sp.peer_memory_available_for(qd, layout):
+            out_p, lse_p = sp.sequence_parallel_forward_p2p(qd, ks, vs, None, causal, layout=layout)
+            fwd_p2p = max((out_p.float() - out[:, rank * sl:(rank + 1) * sl].float()).abs().max().item(),
+                          (lse_p - lse[:, :, rank * sl:(rank + 1) * sl]).abs().max().item())
+            assert fwd_p2p <= 2e-3, fwd_p2p  # zig-zag: parts are merged in one step instead of two
             dq_p, dk_p, dv_p = sp.sequence_parallel_backward_p2p(qd, ks, vs, out, lse, dod, None, causal, layout=layout)
             torch.cuda.synchronize()
             p2p_err = max((dq_p.float() - dq.float()).abs().max().item(), (dk_p.float() - dk.float()).abs().max().item(),
@@ -158,4 +162,6 @@ def test_two_gpu_zigzag_layout_forward_and_backward(d):
         assert status == 0
         # one more fp16 rounding than the contiguous layout: the two chunks' results are merged locally
         assert max(errs) <= 5e-3 + 2.0 ** -9 * scale, (rank, errs, scale)
-    _require_peer_path([results[r][3] for r in range(world)], 1e-6)
+    # the peer-read path sums the four chunk shares in one step, the all-to-all path adds each rank's two
+    # first (one more fp16 rounding): they agree to an fp16 ulp, not bit for bit
+    _require_peer_path([results[r][3] for r in range(world)], 1e-3)
