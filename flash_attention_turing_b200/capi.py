@@ -15,6 +15,7 @@ EXPORTED_SYMBOLS = (
     "fa_last_error",
     "fa_abi_version",
     "fa_device_status",
+    "fa_selftest_wait_timeout",
     "fa_fwd",
     "fa_bwd_workspace_bytes",
     "fa_bwd",
@@ -116,6 +117,8 @@ def lib() -> C.CDLL:
         l.fa_abi_version.restype = C.c_int
         l.fa_device_status.restype = C.c_int
         l.fa_device_status.argtypes = [C.c_int]
+        l.fa_selftest_wait_timeout.restype = C.c_int
+        l.fa_selftest_wait_timeout.argtypes = [C.c_uint32, _vp]
         for name, struct in (("fa_fwd", FaFwdParams), ("fa_bwd", FaBwdParams), ("fa_kvcache", FaKvcacheParams),
                              ("fa_kvcache_noalloc", FaKvcacheParams), ("fa_combine", FaCombineParams)):
             fn = getattr(l, name)

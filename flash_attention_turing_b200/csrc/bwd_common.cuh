@@ -41,6 +41,9 @@ namespace {
 
 constexpr int kBlock = 128;  // tile edge in both sequence dimensions
 constexpr int kNumThreads = 608;  // 16 elementwise warps, TMA producer, two MMA-issuing warps
+// 19 warps: five on one SM sub-partition (16384 registers) -> at most 96 registers per thread, which is what
+// __launch_bounds__(608, 1) makes the compiler use; a larger budget could not be scheduled at all
+static_assert((kNumThreads / 32 + 3) / 4 * 32 * 96 <= 16384, "register file of one SM sub-partition");
 constexpr int kComputeWarps = 16;
 constexpr int kProducerWarp = 16;
 constexpr int kMmaWarp = 17;    // issues the products S, dP (S^T, dP^T) that feed the elementwise warps

@@ -102,10 +102,7 @@ bwd_fused_kernel(const __grid_constant__ BwdKernelParams p) {
   const int sk = varlen ? p.cu_seqlens_k[batch + 1] - k_off : p.seqlen_k;
   const int key0 = nblk * kBlock;
   if (key0 >= sk) return;
-  // read by one thread and broadcast, so that the whole CTA takes the same way out
-  if (__syncthreads_or(threadIdx.x == 0 && p.status &&
-                       (*reinterpret_cast<volatile int*>(p.status) & kStatusWaitTimeout) != 0))
-    return;
+  if (cta_should_stop(p.status)) return;
   const int bq = varlen ? 0 : batch;
   const int group = p.h / p.h_k;
   const int nq = (sq + kBlock - 1) / kBlock;

@@ -120,7 +120,7 @@ bwd_dq_kernel(const __grid_constant__ BwdKernelParams p) {
   const int sk = varlen ? p.cu_seqlens_k[batch + 1] - k_off : p.seqlen_k;
   const int row0 = mblk * kBlock;
   if (row0 >= sq) return;
-  if (p.status && (*reinterpret_cast<volatile int*>(p.status) & kStatusWaitTimeout) != 0) return;
+  if (cta_should_stop(p.status)) return;
   const int bq = varlen ? 0 : batch;
   const int head_k = head / (p.h / p.h_k);
   const int nkb = (sk + kBlock - 1) / kBlock;
@@ -361,7 +361,7 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
   const int sk = varlen ? p.cu_seqlens_k[batch + 1] - k_off : p.seqlen_k;
   const int key0 = nblk * kBlock;
   if (key0 >= sk) return;
-  if (p.status && (*reinterpret_cast<volatile int*>(p.status) & kStatusWaitTimeout) != 0) return;
+  if (cta_should_stop(p.status)) return;
   const int bq = varlen ? 0 : batch;
   const int group = p.h / p.h_k;
   const int nq = (sq + kBlock - 1) / kBlock;

@@ -92,6 +92,10 @@ struct Barriers {
   int abort_flag;
 };
 
+// ten warps: three on one SM sub-partition (16384 registers): 3 x 32 x 168 fits; a budget that does not fit
+// cannot be scheduled at all
+static_assert((kNumThreads / 32 + 3) / 4 * 32 * 168 <= 16384, "register file of one SM sub-partition");
+
 template <int D>
 __global__ void __maxnreg__(168)
 fwd_kernel(const __grid_constant__ FwdKernelParams p) {
@@ -116,7 +120,7 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
   }
   const int row0 = mpair * (kTiles * kBlockM);
   if (row0 >= sq) return;
-  if (p.status && (*reinterpret_cast<volatile int*>(p.status) & kStatusWaitTimeout) != 0) return;
+  if (cta_should_stop(p.status)) return;
 
   const int bq = varlen_q ? 0 : batch;
   const int bk = varlen_k ? 0 : (p.cache_batch_idx ? p.cache_batch_idx[batch] : batch);

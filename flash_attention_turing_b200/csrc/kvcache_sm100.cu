@@ -141,7 +141,8 @@ decode_kernel(const __grid_constant__ DecodeParams p) {
     return (static_cast<int64_t>(batch) * p.h + head) * p.seqlen_q + q_pos;
   };
 
-  if (my_tiles <= 0 || (p.status && (*reinterpret_cast<volatile int*>(p.status) & kStatusWaitTimeout) != 0)) {
+  const bool stop = cta_should_stop(p.status);  // CTA-uniform
+  if (my_tiles <= 0 || stop) {
     // empty split: neutral partial (or a zero row when there is nothing to attend to at all)
     for (int idx = threadIdx.x; idx < rows * (D / 2); idx += blockDim.x) {
       const int r = idx / (D / 2);

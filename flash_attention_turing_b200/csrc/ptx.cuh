@@ -107,11 +107,20 @@ struct WaitCtx {
   int tag = 0;
   const void* base = nullptr;
   int iter = 0;  // loop iteration of the waiting role (bits 25-30), maintained by kernels that want it recorded
+  uint64_t limit_ns = 4000000000ull;  // wall-clock limit of one wait
 };
+
+// The wait-timeout bit of the status word is sticky (until the host clears it): a CTA that starts while it is
+// set does no work.  One thread reads the word and the answer is broadcast, so that the whole CTA takes the
+// same way out even if the bit is set while the CTA starts.
+__device__ __forceinline__ bool cta_should_stop(const int* status) {
+  return __syncthreads_or(threadIdx.x == 0 && status != nullptr &&
+                          (*reinterpret_cast<const volatile int*>(status) & kStatusWaitTimeout) != 0) != 0;
+}
 
 // Bounded wait on an mbarrier phase.  Returns false when the CTA is aborting (this wait or another
 // one ran out of time); the caller must then fall through to the kernel's common exit.
-// Limit: 4 s of wall time measured with %globaltimer, far above any legitimate wait.
+// Limit: ctx.limit_ns of wall time measured with %globaltimer (4 s, far above any legitimate wait).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
   if (mbar_test(bar, parity)) return true;
   uint64_t t0 = 0;
@@ -123,7 +132,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
       uint64_t now = global_timer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > 4000000000ull) {
+      } else if (now - t0 > ctx.limit_ns) {
         *ctx.abort_flag = 1;
         if (ctx.status) {
           int idx = 0;

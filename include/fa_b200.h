@@ -58,9 +58,21 @@ int fa_abi_version(void);
  * dK/dV kernel found its dynamic shared memory not aligned to 1024 bytes (its head-size-128 layout has
  * no room for an alignment pad) and did no work, so dK and dV of that launch are invalid; negative =
  * FA_ERR_*.  With
- * reset != 0 the word is cleared afterwards.  No counterpart in the reference, whose launches are
+ * reset != 0 the word is cleared afterwards.  Bit 0 is STICKY: while it is set, every later forward, backward
+ * or decode launch on that device returns without doing any work (its outputs stay as they were) although the
+ * host call reports FA_OK, until this function clears the word -- a host that wants to detect the condition
+ * polls it.  When a wait gave up, bits 8-31 of the word identify the first one that did: bits 8-15 the warp
+ * role that waited, bits 16-23 the index of the barrier in the kernel's barrier block, bit 24 the phase
+ * parity, bits 25-30 the loop iteration.  No counterpart in the reference, whose launches are
  * not error-checked at all (src/flash_fwd_launch_template.h:73-89). */
 int fa_device_status(int reset);
+
+/* Self-test of the bounded waits: launches one tiny CTA that waits, with a limit of limit_us microseconds
+ * (1 .. 1 000 000) instead of the kernels' 4 s, on a barrier nobody arrives on.  The wait gives up, bit 0 of
+ * the status word is set (bits 8-15 read 0x7f), and the kernel returns normally: the path a real time-out
+ * takes, without a hung launch.  Read and clear the word with fa_device_status(1) afterwards.  No
+ * counterpart in the reference (its kernels have no bounded waits). */
+int fa_selftest_wait_timeout(uint32_t limit_us, fa_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------- */
 /* Forward: O = softmax(Q K^T * scale [+ causal mask]) V, LSE = logsumexp of the scaled scores.  */

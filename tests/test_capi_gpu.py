@@ -198,3 +198,33 @@ def test_fa_kvcache_raw_paged():
         assert err_stats(out, o_ref)[0] <= 2e-3 and err_stats(lse, lse_ref)[0] <= LSE_TOL
     assert torch.equal(kcd.cpu(), kc_ref) and torch.equal(vcd.cpu(), vc_ref)
     assert lib.fa_device_status(1) == 0
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_context_stays_usable():
+    """Failure detection without a failure: fa_selftest_wait_timeout() makes one bounded wait run out after
+    2 ms (a barrier nobody arrives on, the kernels' own wait routine with a short limit).  The kernel returns by
+    itself, bit 0 of the status word is set with the self-test's tag in bits 8-15, a launch issued while the bit
+    is set does no work, and after the word is cleared everything works as before."""
+    from flash_attention_turing_b200 import capi
+
+    lib = capi.lib()
+    assert lib.fa_device_status(1) == 0
+    capi.check(lib.fa_selftest_wait_timeout(2000, _stream()))
+    status = lib.fa_device_status(0)
+    assert status & 1 and (status >> 8) & 0xff == 0x7f, hex(status)
+    # sticky: a forward launched now leaves its output untouched and the host call still reports success
+    b, s, h, d = 1, 128, 1, 64
+    gen = torch.Generator().manual_seed(2)
+    q, k, v = (randn_half(gen, b, s, h, d).to(DEV) for _ in range(3))
+    o = torch.full_like(q, 7.0)
+    lse = torch.empty(b, h, s, dtype=torch.float32, device=DEV)
+    fp = capi.fwd_params(q, k, v, o, lse, d ** -0.5, False)
+    capi.check(lib.fa_fwd(ctypes.byref(fp), _stream()))
+    torch.cuda.synchronize()
+    assert bool((o == 7.0).all())
+    assert lib.fa_device_status(1) & 1  # read and clear
+    assert lib.fa_device_status(0) == 0
+    capi.check(lib.fa_fwd(ctypes.byref(fp), _stream()))
+    o_ref, _ = orc.attention_forward(q.cpu(), k.cpu(), v.cpu(), None, False)
+    assert err_stats(o, o_ref)[0] <= 2e-3
+    assert lib.fa_device_status(1) == 0
