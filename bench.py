@@ -50,10 +50,12 @@ DECODE = dict(b=64, h=32, h_k=8, d=128, page=256, pages=16384, max_pages=129, lo
 METRIC = "attn fwd+bwd TFLOP/s (hd128 causal, S=8k)"
 WORKLOAD_NAME = "H8K: B4 S8192 H32 D128 causal, forward + backward"  # the same string in both arms
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
-# DRAM bytes (read + write) per launch of the kernels at exactly the workloads above, from one profiler capture
-# (dram__bytes_read.sum + dram__bytes_write.sum, one pass).  They are constants of the workload, not measured by
-# this script; algorithmic tensor bytes for comparison: forward 1078 MB, backward 3494 MB, decode 4275 MB.
-NCU_TRAFFIC_BYTES = dict(fwd=1057.6e6, bwd=548.5e6 + 1333.0e6 + 1588.8e6, decode=4285.1e6 + 4.5e6)
+# DRAM bytes (read + write) per launch of the kernels at exactly the workloads above, from profiler captures
+# (dram__bytes_read.sum + dram__bytes_write.sum): the backward kernels from one launch each at full size, the
+# forward and the decode kernel scaled from reduced-case captures by the tensor bytes a launch touches.  They
+# are constants of the workload, not measured by this script; algorithmic tensor bytes for comparison: forward
+# 1078 MB, backward 3494 MB, decode 4275 MB.
+NCU_TRAFFIC_BYTES = dict(fwd=0.87 * 1078e6, bwd=548.5e6 + 1336.4e6 + 1590.1e6, decode=1.002 * 4275.4e6 + 4.5e6)
 
 
 def fwd_flops(b, h, sq, sk, d, causal):
@@ -180,7 +182,23 @@ def run_profile_case(args):
     torch.cuda.set_device(dev)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     gen = torch.Generator(device=dev).manual_seed(5)
-    if args.profile in ("fwd", "bwd"):
+    if args.profile == "bwd_full_size":
+        # ONE launch of each backward path at the benchmark size (B4 S8192 H32 D128 causal; 2.5 GB resident): for
+        # single-pass traffic counters only
+        w = WORKLOAD
+        b, s, h, d = w["b"], w["s"], w["h"], w["d"]
+        q, k, v, dout = (torch.randn(b, s, h, d, device=dev, dtype=torch.half, generator=gen) for _ in range(4))
+        o, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+        lse = torch.empty(b, h, s, device=dev, dtype=torch.float32)
+        capi.check(lib.fa_fwd(ctypes.byref(capi.fwd_params(q, k, v, o, lse, d ** -0.5, True)), stream))
+        for flags in (capi.FA_BWD_SINGLE_KERNEL, 0):
+            bp = capi.bwd_params(q, k, v, o, dout, lse, dq, dk, dv, None, d ** -0.5, True)
+            bp.flags = flags
+            ws = torch.empty(lib.fa_bwd_workspace_bytes(ctypes.byref(bp)), dtype=torch.uint8, device=dev)
+            bp.workspace, bp.workspace_bytes = ws.data_ptr(), ws.numel()
+            capi.check(lib.fa_bwd(ctypes.byref(bp), stream))
+            torch.cuda.synchronize()
+    elif args.profile in ("fwd", "bwd"):
         b, s, h, d = 2, 4096, 16, 128
         q, k, v, dout = (torch.randn(b, s, h, d, device=dev, dtype=torch.half, generator=gen) for _ in range(4))
         o, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
@@ -572,7 +590,7 @@ def main():
     ap.add_argument("--skip-parity", action="store_true")
     ap.add_argument("--skip-configs", action="store_true")
     ap.add_argument("--skip-seq-sharded", action="store_true")
-    ap.add_argument("--profile", choices=["fwd", "bwd", "decode"], default=None,
+    ap.add_argument("--profile", choices=["fwd", "bwd", "decode", "bwd_full_size"], default=None,
                     help="run a few launches of one kernel group on a reduced case and exit (for ncu captures)")
     ap.add_argument("--profile-iters", type=int, default=3)
     ap.add_argument("--bwd-flags", type=int, default=0,

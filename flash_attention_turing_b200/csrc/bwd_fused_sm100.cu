@@ -12,13 +12,21 @@
 //     dK  += dS^T Q_i                 SS (A = the dS^T tile read K-major)
 //     dQ_i partial = dS K             SS (A = the same dS^T tile read MN-major, B = K MN-major); fp32 into
 //                                     the TMEM region of dP^T, which is free once dP^T sits in registers
-// The dQ partial of the pair is read from TMEM by the elementwise warps themselves, in the gap in which they
-// would otherwise wait for the next S^T (one 16x256b load per warp: the 16 warps cover the 128 x D tile), and
-// added to an fp32 accumulator in global memory with red.global.add.v2.f32 (every quad of threads writes one
-// full 32-byte sector); the accumulator of a head stays resident in L2 while its key tiles are processed.  The
-// TMEM region is handed back before the first reduction is issued, so the memory system's pace never holds up
-// the tensor pipe.  The order of the additions depends on scheduling: dQ is NOT bitwise reproducible run to run
-// (dK, dV are).  The two-kernel path (the default; this one is selected with FA_BWD_SINGLE_KERNEL) is bitwise reproducible.
+// The dQ partial of a pair is read from TMEM by the elementwise warps themselves one pair later, right after they
+// have handed over P^T of the next pair (one 16x256b load per warp: the 16 warps cover the 128 x D tile), and added
+// to an fp32 accumulator in global memory with 16-byte reductions (red.global.add.v4.f32); the accumulator is laid
+// out in the order of the TMEM fragments, so a warp's reduction writes 512 contiguous bytes, and the accumulator of
+// a head stays resident in L2 while its key tiles are processed (measured: the 17 GB of reduction traffic of the
+// benchmark shape never reach DRAM).  The TMEM region is handed back before the first reduction is issued.  The
+// order of the additions depends on scheduling: dQ is NOT bitwise reproducible run to run (dK, dV are).
+//
+// This kernel is selected with FA_BWD_SINGLE_KERNEL; the default is the two-kernel path of bwd_sm100.cu, which is
+// bitwise reproducible AND faster on B200 although it executes seven products instead of five: the 64 KB of
+// reductions per pair leave the SM through its load/store unit at about one 32-byte sector per clock (~2000
+// clocks per pair, the `lg_throttle` stall of the profile), and the warps that issue them are the ones the next
+// pair waits for; without the reductions the kernel takes 6.4 ms at B4 S8192 H32 D128, with them 7.4 ms, the two
+// kernels 2.9 + 4.2 ms.  A bulk reduction from shared memory would bypass that unit, but at head size 128 the
+// tiles leave no shared memory to stage it.
 //
 // Warp roles (608 threads, 96 registers): warps 0-15 elementwise math, thread = (key row, 32-query column
 // quarter); warp 16 TMA producer; warp 17 issues S^T and dP^T (the products the elementwise warps wait for) and
@@ -78,9 +86,6 @@ struct FBarriers {
 };
 static_assert(sizeof(FBarriers) <= 512, "barrier block");
 
-__device__ __forceinline__ void red_add_v2(float* addr, float a, float b) {
-  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
-}
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
@@ -235,7 +240,6 @@ bwd_fused_kernel(const __grid_constant__ BwdKernelParams p) {
     // stored in exactly this fragment order, so the 32 threads of a reduction write 512 contiguous bytes.  The TMEM
     // region is handed back (dq_read) before the first reduction is issued.
     auto drain_dq = [&](int it) -> bool {
-#ifndef FA_X_NO_DQ
       const int head = head_k * group + it / per_head;
       const int i = i_min + it % per_head;
       float* a = p.dq_acc + (static_cast<int64_t>(head) * p.dq_acc_rows + (acc_tile0 + i) * kBlock) * D +
@@ -247,15 +251,10 @@ bwd_fused_kernel(const __grid_constant__ BwdKernelParams p) {
       if constexpr (D == 128) tmem_ld_16x256b_x8(taddr, r); else tmem_ld_16x256b_x4(taddr, r);
       tmem_wait_ld();
       warp_arrive_loaded(&bars->dq_read, lane);  // region DP may receive the next dP^T
-#ifndef FA_X_NO_RED
 #pragma unroll
       for (int j = 0; j < D / 16; ++j)
         red_add_v4(a + 128 * j, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
                    __uint_as_float(r[4 * j + 3]));
-#else
-      if (r[0] == 0x12345678u && r[D / 4 - 1] == 0x9abcdef0u) a[0] = 1.f;  // keep the load alive
-#endif
-#endif
       return true;
     };
     bool ok = true;
@@ -309,10 +308,11 @@ bwd_fused_kernel(const __grid_constant__ BwdKernelParams p) {
       tc_fence_after_sync();
       tmem_st16(tP, pk);
       warp_arrive(&bars->p_full, lane);
-#ifdef FA_X_LATE
-      // the dQ partial of the PREVIOUS pair is drained here, while dP^T of this pair is still being computed
+      // The dQ partial of the PREVIOUS pair is drained here: its product finished long ago (no waiting), and the
+      // reductions are issued while dP^T of this pair, which needs the region the partial occupied, is computed.
+      // (Draining at the end of the pair's own iteration makes the warps wait ~1400 clocks for the dQ product
+      // and was 5 % slower.)
       if (it > 0 && !(ok = drain_dq(it - 1))) break;
-#endif
 
       if (!(ok = mbar_wait_warp(&bars->dp_full, it & 1, ctx))) break;
       tc_fence_after_sync();
@@ -349,15 +349,8 @@ bwd_fused_kernel(const __grid_constant__ BwdKernelParams p) {
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->ds_full);
-#ifndef FA_X_LATE
-      // In steady state the next S^T is not ready yet at this point (it waits for the dV MMAs of this pair), so
-      // the read-out of the dQ partial falls into a gap.
-      if (!(ok = drain_dq(it))) break;
-#endif
     }
-#ifdef FA_X_LATE
     if (ok && n_it > 0) ok = drain_dq(n_it - 1);
-#endif
     // ---- epilogue: column quarters 0,1 store the halves of dV, quarters 2,3 the halves of dK * scale ----
     const int which = cq >> 1;        // 0 = dV, 1 = dK
     const int col_half = cq & 1;      // which D/2 columns
@@ -436,9 +429,7 @@ bwd_fused_kernel(const __grid_constant__ BwdKernelParams p) {
           tc_commit(&bars->s_full);
           tc_commit(&bars->q_empty[it % C::kStagesQ]);  // second reader: the dK MMAs of this pair
           // region DP holds the dQ partial of the previous pair until the reduction warps have read it
-#ifndef FA_X_NO_DQ
           if (it > 0 && !(ok = wait(&bars->dq_read, (it - 1) & 1))) break;
-#endif
           tc_fence_after_sync();
           ok = gemm_ss<D>(tmem_base + kFColDP, v_addr, do_tile(it), idesc_nn,  // dP^T = V dO^T
                           [&] { return it + 1 >= n_it || q_full(it + 1); });
@@ -478,12 +469,10 @@ bwd_fused_kernel(const __grid_constant__ BwdKernelParams p) {
           if (fix_k_tail && it == 0 && !(ok = mbar_wait(&bars->k_fixed, 0, ctx))) break;
           tc_fence_after_sync();
           // dQ partial = dS K: contraction over the 128 keys in 8 slices of 16 rows (2048 B) of both tiles
-#ifndef FA_X_NO_DQ
 #pragma unroll
           for (int k = 0; k < 8; ++k)
             mma_ss(tDQ, desc_advance(ds_mnmajor, k * 2048), mnmajor_slice(k_mnmajor, k), idesc_dq, k > 0);
           tc_commit(&bars->dq_full);
-#endif
           // dK += dS^T Q: contraction over the 128 queries; slice k of A = 32 bytes inside the 128-byte rows of
           // chunk k / 4, slice k of B = 16 rows of the Q tile
           const uint64_t q_mnmajor = mnmajor_tile<D>(smem_u32(sQ + sq_ * C::kTileBytes));
