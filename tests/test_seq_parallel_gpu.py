@@ -165,3 +165,63 @@ def test_two_gpu_zigzag_layout_forward_and_backward(d):
     # the peer-read path sums the four chunk shares in one step, the all-to-all path adds each rank's two
     # first (one more fp16 rounding): they agree to an fp16 ulp, not bit for bit
     _require_peer_path([results[r][3] for r in range(world)], 1e-3)
+
+
+@pytest.mark.parametrize("world,layout", [(2, "contiguous"), (4, "contiguous"), (8, "contiguous"), (2, "zigzag"),
+                                          (4, "zigzag"), (8, "zigzag")])
+@pytest.mark.parametrize("d,causal", [(128, True), (64, True), (128, False)])
+def test_sequence_sharded_data_path_on_one_gpu_meets_the_parity_rule(world, layout, d, causal):
+    """The whole device-side data path of the sequence-sharded forward and backward, with the ranks run one
+    after the other on ONE GPU (the merge kernels do not care whose memory a part pointer names): every chunk of
+    every rank is one launch written in place (fp16 partial O, fp32 LSE, fp16 dQ share), fa_combine_gather
+    merges up to 16 parts, fa_sum_gather adds the shares from the first row that sees each chunk.  The partials
+    and shares travel in fp16, so the merged result carries one more fp16 rounding than a single launch: it is
+    held to the same rule as every other result, <= 2 x the reference kernel's own error against fp32."""
+    from flash_attention_turing_b200 import _ext, seq_parallel as sp
+    from helpers import LSE_TOL, assert_within_twice_reference_kernel, emulate_reference_kernel
+    from oracle import attention_oracle as orc
+
+    ext = _ext.load()
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(1000 + world + d)
+    b, s, h, hk = 1, 2048, 4, 2
+    q, k, v, dout = (torch.randn(b, s, n, d, generator=gen).half() for n in (h, hk, hk, h))
+    scale = d ** -0.5
+    qd, dod = q.to(dev), dout.to(dev)
+    nch = 2 if layout == "zigzag" else 1
+    o_bufs = torch.full((world, nch, b, s, h, d), float("nan"), dtype=torch.half, device=dev)
+    l_bufs = torch.full((world, nch, b, h, s), float("nan"), dtype=torch.float32, device=dev)
+    shards = [(sp.shard_kv(k, r, world, layout).to(dev), sp.shard_kv(v, r, world, layout).to(dev)) for r in range(world)]
+    for r, (ks, vs) in enumerate(shards):
+        sp.rank_partials_inplace(qd, ks, vs, r, world, scale, causal, layout, o_bufs[r], l_bufs[r])
+    o_parts = [x for r in range(world) for x in o_bufs[r].unbind(0)]
+    l_parts = [x for r in range(world) for x in l_bufs[r].unbind(0)]
+    sl = s // world
+    outs, lses = zip(*(ext.combine_gather(o_parts, l_parts, r * sl, sl) for r in range(world)))
+    out, lse = torch.cat(outs, 1), torch.cat(lses, 2)
+
+    dq_bufs = torch.full((world, nch, b, s, h, d), float("nan"), dtype=torch.half, device=dev)
+    dks, dvs = [], []
+    for r, (ks, vs) in enumerate(shards):
+        dk, dv = torch.full_like(ks, float("nan")), torch.full_like(vs, float("nan"))
+        sp.rank_backward_inplace(qd, ks, vs, out, lse, dod, r, world, scale, causal, layout, dq_bufs[r], dk, dv)
+        dks.append(dk)
+        dvs.append(dv)
+    parts = [x for r in range(world) for x in dq_bufs[r].unbind(0)]
+    first = sp.chunk_first_rows(world, s, layout, causal)
+    dq = torch.cat([ext.sum_gather(parts, r * sl, sl, first) for r in range(world)], 1)
+    torch.cuda.synchronize()
+    assert ext.device_status(True) == 0
+
+    ref_o, ref_l = orc.attention_forward(q, k, v, scale, causal)
+    rq, rk, rv = orc.attention_backward(q, k, v, dout, scale, causal)
+    em = emulate_reference_kernel(q, k, v, dout, scale, causal)
+    assert (lse.cpu() - ref_l).abs().max().item() <= LSE_TOL
+    assert_within_twice_reference_kernel("O", out, ref_o, em.out)
+    assert_within_twice_reference_kernel("dQ", dq, rq, em.dq)
+    for r in range(world):
+        # a rank's dK / dV rows are final (no exchange): compare shard by shard
+        for name, got, want, emul in (("dK", dks[r], rk, em.dk), ("dV", dvs[r], rv, em.dv)):
+            e = sp.shard_kv(emul.as_subclass(torch.Tensor), r, world, layout).as_subclass(type(emul))
+            e.one_event = getattr(emul, "one_event", 0.0)
+            assert_within_twice_reference_kernel(f"{name}[rank {r}]", got, sp.shard_kv(want, r, world, layout), e)
