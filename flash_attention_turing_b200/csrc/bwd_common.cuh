@@ -4,6 +4,10 @@
 #pragma once
 
 #include "common.h"
+
+// The backward kernels keep the wait loops inline: with 96 registers per thread the call of the out-of-line form
+// costs spills around every wait (measured slower at head size 128).
+#define FA_WAIT_INLINE
 #include "ptx.cuh"
 
 namespace fa {

@@ -15,8 +15,13 @@ thread_local std::string g_last_error;
 // One status word per device; kernels receive its address as a parameter.
 __device__ int g_device_status;
 
+__device__ int g_sched_slots[2 * kSchedSlots];
+
 constexpr int kMaxDevices = 64;
 int* g_status_ptr[kMaxDevices] = {};
+int* g_sched_ptr[kMaxDevices] = {};
+unsigned g_sched_next[kMaxDevices] = {};
+int g_sm_count[kMaxDevices] = {};
 int g_sm100_ok[kMaxDevices] = {};  // 0 unknown, 1 yes, -1 no
 std::mutex g_mutex;
 
@@ -102,6 +107,30 @@ int* device_status_ptr() {
   return g_status_ptr[dev];
 }
 
+int* next_sched_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_sched_ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_sched_slots) != cudaSuccess) return nullptr;
+    g_sched_ptr[dev] = static_cast<int*>(p);
+  }
+  return g_sched_ptr[dev] + 2 * (g_sched_next[dev]++ % kSchedSlots);
+}
+
+int device_sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_sm_count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    g_sm_count[dev] = n;
+  }
+  return g_sm_count[dev];
+}
+
 }  // namespace fa
 
 extern "C" {
@@ -119,6 +148,9 @@ int fa_device_status(int reset) {
   if (reset && value != 0) {
     int zero = 0;
     FA_CHECK_CUDA(cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice));
+    void* slots = nullptr;  // a launch that gave up leaves its work counters dirty
+    FA_CHECK_CUDA(cudaGetSymbolAddress(&slots, fa::g_sched_slots));
+    FA_CHECK_CUDA(cudaMemset(slots, 0, sizeof(int) * 2 * fa::kSchedSlots));
   }
   return value;
 }

@@ -42,6 +42,17 @@ int check_device_sm100();
 // Address of the per-device status word kernels write when a bounded wait gives up.
 int* device_status_ptr();
 
+// Work counters of the persistent kernels: a pool of {next item, finished CTAs} pairs in device memory, all zero
+// between launches (the last CTA of a launch to finish puts its pair back to zero).  Every launch takes the next
+// pair of the pool in turn, so launches that overlap on different streams do not share one unless kSchedSlots
+// launches lie between them.  fa_device_status(1) clears the pool together with a non-zero status word (a
+// launch that gave up on a wait leaves its pair dirty).
+constexpr int kSchedSlots = 1024;
+int* next_sched_slot();
+
+// Number of SMs of the current device (cached); 0 on error.
+int device_sm_count();
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace fa

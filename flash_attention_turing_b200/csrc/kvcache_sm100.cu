@@ -25,6 +25,7 @@
 
 #include "combine.h"
 #include "fwd.h"
+#define FA_WAIT_INLINE  // two waits in all: nothing to gain from the out-of-line form
 #include "ptx.cuh"
 
 namespace fa {
