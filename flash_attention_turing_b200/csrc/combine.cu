@@ -10,6 +10,7 @@
 // LSE = 0 as there (:727).
 #include "combine.h"
 
+#define FA_WAIT_INLINE
 #include "ptx.cuh"
 
 namespace fa {

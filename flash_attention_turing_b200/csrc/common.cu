@@ -1,6 +1,7 @@
 // Host-side helpers: thread-local error text, TMA descriptor encoding through the driver entry
 // point (no link-time dependency on libcuda), device capability check, device status word.
 #include "common.h"
+#define FA_WAIT_INLINE
 #include "ptx.cuh"
 
 #include <cudaTypedefs.h>

@@ -121,18 +121,47 @@ __device__ __forceinline__ bool cta_should_stop(const int* status) {
 // Bounded wait on an mbarrier phase.  Returns false when the CTA is aborting (this wait or another
 // one ran out of time); the caller must then fall through to the kernel's common exit.
 // Limit: ctx.limit_ns of wall time measured with %globaltimer (4 s, far above any legitimate wait).
-// The spin itself is inline (a waiter reacts within one probe of the barrier completing); the bookkeeping that
-// runs once per 1024 probes -- abort flag, clock, time-out record -- is ONE out-of-line function: inlined at
-// every wait it made up a large part of the kernels' code, and the kernels run close to the capacity of the
-// instruction cache (all warp roles execute different code at the same time).
-// mbar_wait_check: `t0` is the time of the first check of this wait (0: this is the first); returns the value to
-// pass next time, or 0 when the wait must be given up.
+//
+// Two forms, chosen per translation unit.  With FA_WAIT_INLINE the whole loop is inline at every wait (the
+// backward kernels: with 96 registers per thread a call inside their loops costs spills, measured 5-25 %
+// slower).  Without it, the bookkeeping that runs once per 1024 probes (abort flag, clock, time-out record) is
+// one out-of-line function, and so is the spin of waits that are not on a critical path: inlined everywhere
+// the loops made up a sixth of the forward kernel's code, which runs close to the capacity of the instruction
+// cache (all warp roles execute different code at the same time; hit rate 82 % inline, 98 % out of line).
 #ifdef FA_WAIT_INLINE
-__device__ __forceinline__
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
+  if (mbar_test(bar, parity)) return true;
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_test(bar, parity)) return true;
+    if (((++spins) & 0x3ff) == 0) {
+      if (*ctx.abort_flag) return false;
+      uint64_t now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > ctx.limit_ns) {
+        *ctx.abort_flag = 1;
+        if (ctx.status) {
+          int idx = 0;
+          if (ctx.base) idx = static_cast<int>((reinterpret_cast<const uint8_t*>(bar) - static_cast<const uint8_t*>(ctx.base)) >> 3) & 0xff;
+          atomicCAS(ctx.status, 0, kStatusWaitTimeout | ((ctx.tag & 0xff) << 8) | (idx << 16) | ((parity & 1) << 24) | ((ctx.iter & 0x3f) << 25));
+          atomicOr(ctx.status, kStatusWaitTimeout);
+        }
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ bool mbar_wait_hot(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
+  return mbar_wait(bar, parity, ctx);
+}
 #else
-static __device__ __noinline__
-#endif
-uint64_t mbar_wait_check(uint64_t* bar, uint32_t parity, const WaitCtx* ctx, uint64_t t0) {
+// `t0` is the time of the first check of this wait (0: this is the first); returns the value to pass next time,
+// or 0 when the wait must be given up.
+static __device__ __noinline__ uint64_t mbar_wait_check(uint64_t* bar, uint32_t parity, const WaitCtx* ctx,
+                                                        uint64_t t0) {
   if (*ctx->abort_flag) return 0;
   const uint64_t now = global_timer_ns() | 1ull;
   if (t0 == 0) return now;
@@ -164,12 +193,7 @@ __device__ __forceinline__ bool mbar_wait_hot(uint64_t* bar, uint32_t parity, co
 
 // For all other waits: the first probe is inline, the whole spin a call (smallest code; the return from the call
 // and the reloads after it cost the waiter some tens of clocks when the barrier completes).
-#ifdef FA_WAIT_INLINE
-__device__ __forceinline__
-#else
-static __device__ __noinline__
-#endif
-bool mbar_wait_spin(uint64_t* bar, uint32_t parity, const WaitCtx* ctx) {
+static __device__ __noinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, const WaitCtx* ctx) {
   return mbar_wait_hot(bar, parity, *ctx);
 }
 
@@ -177,6 +201,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   if (mbar_test(bar, parity)) return true;
   return mbar_wait_spin(bar, parity, &ctx);
 }
+#endif
 
 // Warp-collective form: every lane waits, and the warp agrees on the outcome so that it stays
 // converged for the .sync.aligned instructions that follow.
