@@ -74,8 +74,9 @@ struct FwdKernelParams {
   int page_size;
   int* status;
   int* sched;         // {next item - gridDim.x, CTAs finished}: both zero at launch and again at the end
-  int items_x;        // work items per (sequence, head): ceil(seqlen_q / 256)
-  int total_items;    // items_x * h * b
+  int items_x;        // dense: work items per (sequence, head) = ceil(seqlen_q / 256)
+  int total_items;    // dense: items_x * h * b; packed sequences: h * (total_q / 256 + b), see the scheduler
+  int b;              // sequences
 };
 
 template <int D>
@@ -243,6 +244,7 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
       // claimed work while another runs dry at the end of the launch (claiming one or two items ahead cost
       // 7 % at sequence length 65536).
       bool finished = false;
+      int seq = 0;  // packed sequences: the sequence of the last claimed index
       for (int n = 0;; ++n) {
         const int slot = n % kSchedDepth;
         int next = blockIdx.x;  // the first item of a CTA needs no counter
@@ -253,11 +255,26 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
         WorkItem it;
         it.batch = 0, it.head = 0, it.mpair = -1, it.pad = 0;
         while (next < p.total_items) {
-          const int x = next % p.items_x, rest = next / p.items_x;
-          const int head = rest % p.h, batch = rest / p.h;
-          const int mpair = p.items_x - 1 - x;  // heavy (late-row) causal items of a head first
+          int batch, head, mpair;
+          if (p.cu_seqlens_q == nullptr) {
+            const int x = next % p.items_x, rest = next / p.items_x;
+            head = rest % p.h, batch = rest / p.h;
+            mpair = p.items_x - 1 - x;  // heavy (late-row) causal items of a head first
+          } else {
+            // Packed sequences: sequence k owns the slots [h * v(k), h * v(k+1)) with v(k) = cu_seqlens_q[k] / 256 + k,
+            // which are at least h * ceil(length / 256) and at most h more -- so an index maps to a live item
+            // except for at most one slot per (sequence, head), whatever the spread of the lengths.  The indices
+            // a CTA claims only grow, so the sequence is found by walking forward from the last one.
+            while (seq + 1 < p.b && p.h * ((p.cu_seqlens_q[seq + 1] >> 8) + seq + 1) <= next) ++seq;
+            const int v0 = (p.cu_seqlens_q[seq] >> 8) + seq, v1 = (p.cu_seqlens_q[seq + 1] >> 8) + seq + 1;
+            const int rel = next - p.h * v0, cnt = v1 - v0;
+            const int len = p.cu_seqlens_q[seq + 1] - p.cu_seqlens_q[seq];
+            batch = seq, head = rel / cnt;
+            mpair = (len + kTiles * kBlockM - 1) / (kTiles * kBlockM) - 1 - rel % cnt;  // < 0: the spare slot
+            if (head >= p.h) mpair = -1;  // past the last sequence
+          }
           const int sq = p.cu_seqlens_q ? p.cu_seqlens_q[batch + 1] - p.cu_seqlens_q[batch] : p.seqlen_q;
-          if (mpair * (kTiles * kBlockM) < sq) {
+          if (mpair >= 0 && mpair * (kTiles * kBlockM) < sq) {
             it.batch = batch, it.head = head, it.mpair = mpair;
             if (p.seqused_k && p.status && head == 0 && mpair == 0) {
               const int raw = p.seqused_k[batch] + p.seqused_k_add;
@@ -265,7 +282,7 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
             }
             break;
           }
-          next = gridDim.x + atomicAdd(p.sched, 1);  // rows past the end of a packed sequence: skip
+          next = gridDim.x + atomicAdd(p.sched, 1);  // a spare slot: skip
         }
         if (!mbar_wait(&bars->sched_empty[slot], ((n / kSchedDepth) & 1) ^ 1, ctx)) break;
         bars->items[slot] = it;
@@ -698,7 +715,7 @@ fwd_kernel(const __grid_constant__ FwdKernelParams p) {
 }
 
 template <int D>
-int launch_fwd(FwdKernelParams& kp, int b, int h, int seqlen_q, cudaStream_t stream) {
+int launch_fwd(FwdKernelParams& kp, int b, int h, int seqlen_q, int64_t total_q, cudaStream_t stream) {
   using C = Cfg<D>;
   static bool configured[64] = {};
   int dev = 0;
@@ -712,7 +729,9 @@ int launch_fwd(FwdKernelParams& kp, int b, int h, int seqlen_q, cudaStream_t str
   kp.sched = next_sched_slot();
   if (sms <= 0 || kp.sched == nullptr) return set_error(FA_ERR_CUDA, "fa_fwd: device attributes not available");
   kp.items_x = (seqlen_q + kTiles * kBlockM - 1) / (kTiles * kBlockM);
-  const int64_t total = static_cast<int64_t>(kp.items_x) * h * b;
+  kp.b = b;
+  const int64_t total = kp.cu_seqlens_q ? static_cast<int64_t>(h) * (total_q / (kTiles * kBlockM) + b)
+                                        : static_cast<int64_t>(kp.items_x) * h * b;
   FA_CHECK_ARG(total < (1ll << 30), "fa_fwd: too many work items");
   kp.total_items = static_cast<int>(total);
   const int grid = kp.total_items < sms ? kp.total_items : sms;  // one CTA per SM (202 KB of shared memory each)
@@ -807,8 +826,8 @@ int run_fwd(const FaFwdParams* p, int seqused_k_add, cudaStream_t stream) {
   kp.page_size = p->page_size;
   kp.status = device_status_ptr();
 
-  if (p->d == 128) return launch_fwd<128>(kp, p->b, p->h, p->seqlen_q, stream);
-  return launch_fwd<64>(kp, p->b, p->h, p->seqlen_q, stream);
+  if (p->d == 128) return launch_fwd<128>(kp, p->b, p->h, p->seqlen_q, p->total_q, stream);
+  return launch_fwd<64>(kp, p->b, p->h, p->seqlen_q, p->total_q, stream);
 }
 
 }  // namespace fa
