@@ -523,3 +523,68 @@ def test_guard_bands_around_outputs_and_scratch(b, sq, sk, h, hk, d, causal, fla
         _check(name, got, want, emu)
     assert err_stats(lse, lse_ref)[0] <= LSE_TOL
     assert lib.fa_device_status(1) == 0
+
+
+def _multi_wave_case(seed, causal=True, d=128):
+    """More work items than SMs, so that the forward takes its items from the global work counter."""
+    gen = torch.Generator().manual_seed(seed)
+    b, s, h, hk = 2, 2048, 12, 4   # 2 x 12 x 8 = 192 items of 256 rows
+    q, k, v = randn_half(gen, b, s, h, d), randn_half(gen, b, s, hk, d), randn_half(gen, b, s, hk, d)
+    return q.to(DEV), k.to(DEV), v.to(DEV), d ** -0.5, causal
+
+
+def test_forward_work_counters_are_left_clean_over_many_launches(ext):
+    """The persistent forward takes a {next item, finished CTAs} pair from a pool of 1024 and its last CTA puts
+    the pair back to zero.  2200 launches go round the pool twice: a pair left dirty by an earlier launch would
+    make a later one skip items, i.e. leave rows of O unwritten."""
+    q, k, v, scale, causal = _multi_wave_case(31)
+    want, want_lse = ext.fwd(q, k, v, scale, causal)
+    out, lse = torch.empty_like(want), torch.empty_like(want_lse)
+    for i in range(2200):
+        if i % 550 == 0:
+            out.fill_(float("nan"))
+        ext.fwd(q, k, v, scale, causal, out=out, lse=lse)
+        if i % 550 == 549:
+            assert torch.equal(out, want) and torch.equal(lse, want_lse), i
+    assert ext.device_status(True) == 0
+
+
+def test_forward_launches_on_two_streams_do_not_share_work_counters(ext):
+    q, k, v, scale, causal = _multi_wave_case(32)
+    q2, k2, v2, _, _ = _multi_wave_case(33, causal=False)
+    want, _ = ext.fwd(q, k, v, scale, causal)
+    want2, _ = ext.fwd(q2, k2, v2, scale, False)
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    outs = []
+    for _ in range(20):  # launches of the two streams overlap on the GPU (each fills it for ~30 us)
+        with torch.cuda.stream(s1):
+            o1, _ = ext.fwd(q, k, v, scale, causal)
+        with torch.cuda.stream(s2):
+            o2, _ = ext.fwd(q2, k2, v2, scale, False)
+        outs.append((o1, o2))
+    torch.cuda.synchronize()
+    for o1, o2 in outs:
+        assert torch.equal(o1, want) and torch.equal(o2, want2)
+    assert ext.device_status(True) == 0
+
+
+def test_forward_in_a_cuda_graph_replays(ext):
+    """A captured launch keeps the counter pair it was given; it is clean again whenever a replay ends, so the
+    graph can be replayed any number of times (new inputs written into the captured tensors)."""
+    q, k, v, scale, causal = _multi_wave_case(34)
+    out = torch.empty_like(q)
+    lse = torch.empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32, device=DEV)
+    ext.fwd(q, k, v, scale, causal, out=out, lse=lse)  # first launch on this device outside the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ext.fwd(q, k, v, scale, causal, out=out, lse=lse)
+    gen = torch.Generator().manual_seed(35)
+    for _ in range(5):
+        q.copy_(randn_half(gen, *q.shape))
+        graph.replay()
+        got = out.clone()
+        want, _ = ext.fwd(q, k, v, scale, causal)
+        assert torch.equal(got, want)
+    assert ext.device_status(True) == 0
