@@ -521,13 +521,25 @@ def measure_seq_sharded(ext, dev, rank, world, iters=3):
         if layout not in peer_ok:
             peer_ok[layout] = sp.peer_memory_available_for(q, layout)
         if peer_ok[layout]:
-            o_p, l_p = sp.sequence_parallel_forward_p2p(q, ks, vs, scale, True, layout=layout)
-            ent["fwd_peer_read_ms"] = timed(lambda: sp.sequence_parallel_forward_p2p(q, ks, vs, scale, True, layout=layout))
-            ent["fwd_peer_read_max_abs_diff_vs_all_to_all"] = maxall((o_p.float() - out.float()).abs().max().item())
-            dq_p, _, _ = sp.sequence_parallel_backward_p2p(q, ks, vs, out_all, lse_all, do, scale, True, layout=layout)
+            # with zig-zag K/V chunks the rank also produces zig-zag ROWS (chunks r and 2*world-1-r): under the
+            # causal mask that gives every rank the same number of parts to fetch and merge
+            rl = layout
+            want_o = sp.gather_owned_rows(out_all, rank, world, rl)
+            dq_all = [torch.empty_like(dq) for _ in range(world)]
+            dist.all_gather(dq_all, dq)
+            want_dq = sp.gather_owned_rows(torch.cat(dq_all, dim=1), rank, world, rl)
+            del dq_all
+            o_p, l_p = sp.sequence_parallel_forward_p2p(q, ks, vs, scale, True, layout=layout, row_layout=rl)
+            ent["fwd_peer_read_ms"] = timed(lambda: sp.sequence_parallel_forward_p2p(q, ks, vs, scale, True, layout=layout,
+                                                                                      row_layout=rl))
+            ent["fwd_peer_read_max_abs_diff_vs_all_to_all"] = maxall((o_p.float() - want_o.float()).abs().max().item())
+            dq_p, _, _ = sp.sequence_parallel_backward_p2p(q, ks, vs, out_all, lse_all, do, scale, True, layout=layout,
+                                                           row_layout=rl)
             ent["bwd_peer_read_ms"] = timed(lambda: sp.sequence_parallel_backward_p2p(q, ks, vs, out_all, lse_all, do, scale,
-                                                                                       True, layout=layout))
-            ent["dq_peer_read_max_abs_diff_vs_all_to_all"] = maxall((dq_p.float() - dq.float()).abs().max().item())
+                                                                                       True, layout=layout, row_layout=rl))
+            ent["dq_peer_read_max_abs_diff_vs_all_to_all"] = maxall((dq_p.float() - want_dq.float()).abs().max().item())
+            ent["peer_read_rows"] = rl
+            del want_o, want_dq
             ent["peer_read"] = "symmetric memory, plain loads over NVLink"
         else:
             ent["peer_read"] = "unavailable: " + (sp.last_peer_memory_error() or "a peer could not map the buffers")[:200]

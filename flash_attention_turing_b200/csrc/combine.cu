@@ -83,9 +83,23 @@ combine_kernel(const float* __restrict__ o_accum, const float* __restrict__ lse_
   if (lse != nullptr && lane == 0) lse[row] = empty ? 0.f : lse_total;
 }
 
-// Merge over ranks with the partials read in place (possibly from peer GPUs): one warp per output row
-// (b, row, h); the per-rank LSEs sit in the lanes and are reduced with shuffles, every lane then owns D/32
-// consecutive columns of the fp16 partial rows (one 128- or 256-byte coalesced read per rank and row).
+// Merge over ranks with the partials read in place (possibly from peer GPUs): D/8 lanes per output row
+// (b, row, h); the per-part LSEs sit in the lanes of the row's group and are reduced with shuffles, every lane then
+// owns 8 consecutive columns of the fp16 partial rows (16-byte reads, a row is one contiguous 128 or 256 bytes).
+__device__ __forceinline__ uint4 load16_if(const void* ptr, bool pred) {
+  uint4 v = make_uint4(0, 0, 0, 0);
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "@p ld.global.v4.u32 {%0, %1, %2, %3}, [%4];\n\t"
+      "}\n"
+      : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+      : "l"(ptr), "r"(static_cast<int>(pred))
+      : "memory");
+  return v;
+}
+
 struct GatherArgs {
   const __half* o_part[FA_MAX_GATHER_PARTS];
   const float* lse_part[FA_MAX_GATHER_PARTS];
@@ -95,57 +109,87 @@ template <int D>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 combine_gather_kernel(const __grid_constant__ GatherArgs a, __half* __restrict__ o, float* __restrict__ lse,
                       int num_parts, int b, int h, int seqlen_q, int row_begin, int rows) {
-  constexpr int kPerLane = D / 32;
+  // D/8 lanes per output row, 16 bytes per lane: a warp merges 2 (D = 128) or 4 (D = 64) rows.  The parts of a
+  // row are fetched in batches of eight loads issued back to back before any of them is used: the reads go to
+  // other GPUs' memory over NVLink (microseconds of latency), so what matters is the number of bytes in flight.
+  constexpr int kLanes = D / 8;           // lanes per row
+  constexpr int kRows = 32 / kLanes;      // rows per warp
   const int lane = threadIdx.x & 31;
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int sub = lane % kLanes, rsel = lane / kLanes;
   const int64_t total = static_cast<int64_t>(b) * rows * h;
-  if (idx >= total) return;
-  const int head = static_cast<int>(idx % h);
-  const int r = static_cast<int>((idx / h) % rows);
-  const int batch = static_cast<int>(idx / (static_cast<int64_t>(h) * rows));
+  const int64_t idx = (static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5)) * kRows + rsel;
+  const bool live = idx < total;
+  const int64_t id = live ? idx : total - 1;  // dead lanes repeat the last row (shuffles need every lane)
+  const int head = static_cast<int>(id % h);
+  const int r = static_cast<int>((id / h) % rows);
+  const int batch = static_cast<int>(id / (static_cast<int64_t>(h) * rows));
   const int64_t lse_idx = (static_cast<int64_t>(batch) * h + head) * seqlen_q + row_begin + r;
-  const int64_t o_idx = ((static_cast<int64_t>(batch) * seqlen_q + row_begin + r) * h + head) * D + lane * kPerLane;
+  const int64_t o_idx = ((static_cast<int64_t>(batch) * seqlen_q + row_begin + r) * h + head) * D + sub * 8;
 
-  float my = (lane < num_parts) ? a.lse_part[lane][lse_idx] : -INFINITY;
-  float mx = my;
+  // the LSEs of the parts sit in the lanes of the row's group (part p in lane p and, for D = 64 with more than
+  // eight parts, in a second round)
+  float mx = -INFINITY;
+  float my[(FA_MAX_GATHER_PARTS + kLanes - 1) / kLanes];
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-  float e = (mx == -INFINITY || my == -INFINITY) ? 0.f : __expf(my - mx);
-  float sum = e;
+  for (int k = 0; k < (FA_MAX_GATHER_PARTS + kLanes - 1) / kLanes; ++k) {
+    const int part = k * kLanes + sub;
+    my[k] = (part < num_parts) ? a.lse_part[part][lse_idx] : -INFINITY;
+    mx = fmaxf(mx, my[k]);
+  }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  for (int off = kLanes / 2; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  float e[(FA_MAX_GATHER_PARTS + kLanes - 1) / kLanes];
+  float sum = 0.f;
+#pragma unroll
+  for (int k = 0; k < (FA_MAX_GATHER_PARTS + kLanes - 1) / kLanes; ++k) {
+    e[k] = (mx == -INFINITY || my[k] == -INFINITY) ? 0.f : __expf(my[k] - mx);
+    sum += e[k];
+  }
+#pragma unroll
+  for (int off = kLanes / 2; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
   const bool empty = (mx == -INFINITY) || (sum == 0.f);
-  const float w_mine = empty ? 0.f : e / sum;  // weight of part `lane`
+  const float inv = empty ? 0.f : 1.f / sum;
 
-  float acc[kPerLane];
+  float acc[8];
 #pragma unroll
-  for (int i = 0; i < kPerLane; ++i) acc[i] = 0.f;
-  for (int part = 0; part < num_parts; ++part) {
-    const float w = __shfl_sync(0xffffffffu, w_mine, part);
-    if (w == 0.f) continue;
-    const __half* src = a.o_part[part] + o_idx;
-    if constexpr (kPerLane == 4) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(src);
-      const float2 x0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-      const float2 x1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-      acc[0] = fmaf(w, x0.x, acc[0]); acc[1] = fmaf(w, x0.y, acc[1]);
-      acc[2] = fmaf(w, x1.x, acc[2]); acc[3] = fmaf(w, x1.y, acc[3]);
-    } else {
-      const uint32_t raw = *reinterpret_cast<const uint32_t*>(src);
-      const float2 x0 = __half22float2(*reinterpret_cast<const __half2*>(&raw));
-      acc[0] = fmaf(w, x0.x, acc[0]); acc[1] = fmaf(w, x0.y, acc[1]);
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int p0 = 0; p0 < num_parts; p0 += 8) {
+    uint4 raw[8];
+    float w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int part = p0 + i;  // uniform over the warp
+      // weight of `part` for this lane's row: held by lane (part % kLanes) of the row's group in round part / kLanes
+      float wk = 0.f;
+#pragma unroll
+      for (int k = 0; k < (FA_MAX_GATHER_PARTS + kLanes - 1) / kLanes; ++k) {
+        const float v = __shfl_sync(0xffffffffu, e[k], rsel * kLanes + (part % kLanes));
+        if (k == part / kLanes) wk = v;
+      }
+      w[i] = (part < num_parts) ? wk * inv : 0.f;
+      // predicated, not branched: the eight loads of a batch are issued back to back; parts without keys for
+      // this row (weight 0) are not read at all
+      raw[i] = load16_if(part < num_parts ? a.o_part[part] + o_idx : nullptr, w[i] != 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t u[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&u[c]));
+        acc[2 * c] = fmaf(w[i], x.x, acc[2 * c]);
+        acc[2 * c + 1] = fmaf(w[i], x.y, acc[2 * c + 1]);
+      }
     }
   }
-  __half* dst = o + ((static_cast<int64_t>(batch) * rows + r) * h + head) * D + lane * kPerLane;
-  if constexpr (kPerLane == 4) {
-    uint2 v;
-    v.x = pack_half2(acc[0], acc[1]);
-    v.y = pack_half2(acc[2], acc[3]);
-    *reinterpret_cast<uint2*>(dst) = v;
-  } else {
-    *reinterpret_cast<uint32_t*>(dst) = pack_half2(acc[0], acc[1]);
-  }
-  if (lane == 0) lse[(static_cast<int64_t>(batch) * h + head) * rows + r] = empty ? 0.f : mx + __logf(sum);
+  if (!live) return;
+  uint4 v;
+  v.x = pack_half2(acc[0], acc[1]);
+  v.y = pack_half2(acc[2], acc[3]);
+  v.z = pack_half2(acc[4], acc[5]);
+  v.w = pack_half2(acc[6], acc[7]);
+  *reinterpret_cast<uint4*>(o + ((static_cast<int64_t>(batch) * rows + r) * h + head) * D + sub * 8) = v;
+  if (sub == 0) lse[(static_cast<int64_t>(batch) * h + head) * rows + r] = empty ? 0.f : mx + __logf(sum);
 }
 
 // out[b, r, :] = sum over parts of part[b, row_begin + r, :] (fp32 sum of fp16 values); one thread per 8
@@ -166,15 +210,26 @@ sum_gather_kernel(const __grid_constant__ SumArgs a, __half* __restrict__ out, i
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-  for (int part = 0; part < num_parts; ++part) {
-    if (row < a.first_row[part]) continue;
-    const uint4 raw = reinterpret_cast<const uint4*>(a.part[part])[src];
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  // eight predicated loads issued back to back per batch (the parts may be other GPUs' memory: what matters is
+  // the number of bytes in flight); a part is not read below its first valid row.  The additions keep the order
+  // of the parts, so the result does not depend on the batching.
+  for (int p0 = 0; p0 < num_parts; p0 += 8) {
+    uint4 raw[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-      acc[2 * i] += x.x;
-      acc[2 * i + 1] += x.y;
+    for (int i = 0; i < 8; ++i) {
+      const int part = p0 + i;
+      const bool use = part < num_parts && row >= a.first_row[part & (FA_MAX_GATHER_PARTS - 1)];
+      raw[i] = load16_if(use ? reinterpret_cast<const uint4*>(a.part[part]) + src : nullptr, use);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&w[c]));
+        acc[2 * c] += x.x;
+        acc[2 * c + 1] += x.y;
+      }
     }
   }
   uint4 v;
@@ -242,16 +297,17 @@ extern "C" int fa_combine_gather(const FaCombineGatherParams* p, fa_stream_t str
   }
   for (int i = 0; i < p->num_parts; ++i) {
     FA_CHECK_ARG(p->o_part[i] && p->lse_part[i], "fa_combine_gather: NULL partial pointer");
-    FA_CHECK_ARG((reinterpret_cast<uintptr_t>(p->o_part[i]) & 7) == 0, "fa_combine_gather: partials must be 8-byte aligned");
+    FA_CHECK_ARG(aligned16(p->o_part[i]), "fa_combine_gather: partials must be 16-byte aligned");
     a.o_part[i] = static_cast<const __half*>(p->o_part[i]);
     a.lse_part[i] = p->lse_part[i];
   }
-  FA_CHECK_ARG((reinterpret_cast<uintptr_t>(p->o) & 7) == 0, "fa_combine_gather: o must be 8-byte aligned");
+  FA_CHECK_ARG(aligned16(p->o), "fa_combine_gather: o must be 16-byte aligned");
   int rc = check_device_sm100();
   if (rc != FA_OK) return rc;
   const int64_t total = static_cast<int64_t>(p->b) * p->rows * p->h;
   if (total == 0) return FA_OK;
-  const unsigned blocks = static_cast<unsigned>((total + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  const int rows_per_block = kWarpsPerBlock * (32 / (p->d / 8));
+  const unsigned blocks = static_cast<unsigned>((total + rows_per_block - 1) / rows_per_block);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p->d == 128)
     combine_gather_kernel<128><<<blocks, kWarpsPerBlock * 32, 0, s>>>(a, static_cast<__half*>(p->o), p->lse, p->num_parts,

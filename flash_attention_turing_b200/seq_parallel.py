@@ -380,9 +380,27 @@ def last_peer_memory_error() -> str:
     return _last_p2p_error[0]
 
 
+def owned_rows(rank: int, world: int, seqlen: int, row_layout: str = "contiguous"):
+    """The query rows whose final result a rank produces, as (begin, end) ranges in output order: one contiguous
+    slice, or with row_layout="zigzag" the rows of chunks ``rank`` and ``2 * world - 1 - rank`` of 2 * world equal
+    chunks.  Under a causal mask the late rows see every K/V chunk and the early rows one or two, so with
+    contiguous slices the last rank merges (and fetches over NVLink) almost twice the average and the first
+    almost nothing; the zig-zag rows give every rank the same amount."""
+    if _check_layout(row_layout):
+        return shard_chunks(rank, world, seqlen, "zigzag")
+    sl = seqlen // world
+    return [(rank * sl, (rank + 1) * sl)]
+
+
+def gather_owned_rows(x: torch.Tensor, rank: int, world: int, row_layout: str = "contiguous", dim: int = 1):
+    """The rows of a full-length tensor that ``owned_rows`` assigns to a rank, in output order."""
+    return torch.cat([x.narrow(dim, b, e - b) for b, e in owned_rows(rank, world, x.shape[dim], row_layout)], dim=dim)
+
+
 def sequence_parallel_forward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor,
                                   softmax_scale: Optional[float] = None, causal: bool = False,
-                                  group: Optional[dist.ProcessGroup] = None, layout: str = "contiguous"):
+                                  group: Optional[dist.ProcessGroup] = None, layout: str = "contiguous",
+                                  row_layout: str = "contiguous"):
     """Same result as ``sequence_parallel_forward`` (this rank's query-row slice), but without the
     all-to-all: the partials are written into symmetric memory, a device-side barrier orders the ranks,
     and ONE kernel (``fa_combine_gather``) reads the query-row slice of every rank's partial straight from
@@ -410,13 +428,15 @@ def sequence_parallel_forward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_shar
     # one launch per chunk, written straight into the symmetric buffers; each chunk of each rank is one part of
     # the merge (no local pre-merge of the two zig-zag chunks), dead rows are skipped through LSE = -inf
     rank_partials_inplace(q, k_shard, v_shard, rank, world, scale, causal, layout, o_buf, l_buf)
-    sl = s // world
+    mine = owned_rows(rank, world, s, row_layout)  # (see there; output rows in this order)
     hdl_o.barrier(channel=0)  # every rank's partial is complete and visible
     try:
-        out, lse = ext.combine_gather(o_parts, l_parts, rank * sl, sl)
+        res = [ext.combine_gather(o_parts, l_parts, rb, re - rb) for rb, re in mine]
     finally:
         hdl_o.barrier(channel=1)  # nobody overwrites a partial that a peer is still reading
-    return out, lse
+    if len(res) == 1:
+        return res[0]
+    return torch.cat([r[0] for r in res], dim=1), torch.cat([r[1] for r in res], dim=2)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -544,7 +564,7 @@ def sequence_parallel_backward(q: torch.Tensor, k_shard: torch.Tensor, v_shard: 
 def sequence_parallel_backward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, out: torch.Tensor,
                                    lse: torch.Tensor, dout: torch.Tensor, softmax_scale: Optional[float] = None,
                                    causal: bool = False, group: Optional[dist.ProcessGroup] = None,
-                                   layout: str = "contiguous"):
+                                   layout: str = "contiguous", row_layout: str = "contiguous"):
     """Same result as ``sequence_parallel_backward`` without the all-to-all: the dQ shares are written into
     symmetric memory, a device-side barrier orders the ranks, and ONE kernel (``fa_sum_gather``) reads the
     query-row slice of every rank's share straight from that rank's HBM over NVLink (plain loads, no
@@ -568,10 +588,11 @@ def sequence_parallel_backward_p2p(q: torch.Tensor, k_shard: torch.Tensor, v_sha
     # one launch per chunk; the dQ share of every chunk of every rank is one part of the sum, valid from the
     # first row that sees the chunk (rows below are neither written here nor read over NVLink there)
     rank_backward_inplace(q, k_shard, v_shard, out, lse, dout, rank, world, scale, causal, layout, buf, dk, dv)
-    sl = s // world
+    mine = owned_rows(rank, world, s, row_layout)
+    firsts = chunk_first_rows(world, s, layout, causal)
     hdl.barrier(channel=0)  # every rank's share is complete and visible
     try:
-        dq = ext.sum_gather(parts, rank * sl, sl, chunk_first_rows(world, s, layout, causal))
+        res = [ext.sum_gather(parts, rb, re - rb, firsts) for rb, re in mine]
     finally:
         hdl.barrier(channel=1)  # nobody overwrites a share that a peer is still reading
-    return dq, dk, dv
+    return (res[0] if len(res) == 1 else torch.cat(res, dim=1)), dk, dv

@@ -120,6 +120,18 @@ def _bwd_worker(rank, world, port, causal, d, results, layout="contiguous"):
             torch.cuda.synchronize()
             p2p_err = max((dq_p.float() - dq.float()).abs().max().item(), (dk_p.float() - dk.float()).abs().max().item(),
                           (dv_p.float() - dv.float()).abs().max().item())
+            if layout == "zigzag":
+                # zig-zag ROWS as well: the rank produces the rows of chunks r and 2 * world - 1 - r
+                out_z, lse_z = sp.sequence_parallel_forward_p2p(qd, ks, vs, None, causal, layout=layout, row_layout="zigzag")
+                dq_z, _, _ = sp.sequence_parallel_backward_p2p(qd, ks, vs, out, lse, dod, None, causal, layout=layout,
+                                                               row_layout="zigzag")
+                torch.cuda.synchronize()
+                dq_all = [torch.empty_like(dq) for _ in range(world)]
+                dist.all_gather(dq_all, dq)
+                rows_err = max((out_z.float() - sp.gather_owned_rows(out, rank, world, "zigzag").float()).abs().max().item(),
+                               (lse_z - sp.gather_owned_rows(lse, rank, world, "zigzag", dim=2)).abs().max().item(),
+                               (dq_z.float() - sp.gather_owned_rows(torch.cat(dq_all, 1), rank, world, "zigzag").float()).abs().max().item())
+                assert rows_err <= 2e-3, rows_err
         rq, rk, rv = orc.attention_backward(q, k, v, dout, None, causal)
         ref_out, _ = orc.attention_forward(q, k, v, None, causal)
         errs = ((dq.float().cpu() - rq[:, rank * sl:(rank + 1) * sl]).abs().max().item(),
