@@ -588,3 +588,32 @@ def test_forward_in_a_cuda_graph_replays(ext):
         want, _ = ext.fwd(q, k, v, scale, causal)
         assert torch.equal(got, want)
     assert ext.device_status(True) == 0
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("h,hk,d", [(3, 1, 128), (4, 4, 64)])
+def test_varlen_forward_many_ragged_sequences(ext, h, hk, d, causal):
+    """The forward's work-item mapping for packed sequences (slots from cu_seqlens_q / 256) over 70 sequences with
+    the lengths that matter to it: empty ones, single rows, exact multiples of 256 and of 128, one row more or
+    less, and long ones -- more items than SMs, so that the counter path runs.  Every sequence must equal the
+    dense launch on that sequence alone (same kernel, same rounding: bit for bit), which is compared with the
+    oracle elsewhere; LSE padding stays zero."""
+    gen = torch.Generator().manual_seed(77 + d)
+    lens = [0, 1, 255, 256, 257, 511, 512, 513, 128, 127, 129, 0, 0, 3, 1024, 2047, 2048, 2049, 5, 640]
+    lens += [int(x) for x in torch.randint(1, 700, (50,), generator=gen)]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    total = int(cu[-1])
+    q, k, v = randn_half(gen, total, h, d).to(DEV), randn_half(gen, total, hk, d).to(DEV), randn_half(gen, total, hk, d).to(DEV)
+    scale = d ** -0.5
+    out, lse = ext.varlen_fwd(q, k, v, cu.to(DEV), cu.to(DEV), max(lens), max(lens), scale, causal)
+    assert not torch.isnan(out).any()
+    for i, n in enumerate(lens):
+        a, b = int(cu[i]), int(cu[i + 1])
+        if n == 0:
+            assert lse[i].abs().max().item() == 0
+            continue
+        o1, l1 = ext.fwd(q[a:b].unsqueeze(0), k[a:b].unsqueeze(0), v[a:b].unsqueeze(0), scale, causal)
+        assert torch.equal(out[a:b], o1[0]), (i, n)
+        assert torch.equal(lse[i, :, :n], l1[0]), (i, n)
+        assert lse[i, :, n:].abs().max().item() == 0 if n < max(lens) else True
+    assert ext.device_status(True) == 0
