@@ -81,6 +81,12 @@ int fa_selftest_wait_timeout(uint32_t limit_us, fa_stream_t stream);
 /* (src/flash_fwd_launch_template.h:49-93) and flash_fwd_kernel (src/flash_fwd_kernel.h:23-664). */
 /* Also serves the tiled path of mha_fwd_kvcache (flash_api.cpp:686-714) through seqused_k,      */
 /* cache_batch_idx and block_table, without the index_select copy the reference makes.           */
+/* The kernel is persistent: one CTA per SM takes 256-row work items from a counter in device    */
+/* memory (a pool of 1024 counter pairs inside the library; a launch takes the next pair and     */
+/* leaves it zero), where the reference launches one CTA per row block of a max_seqlen-sized     */
+/* grid (src/flash_fwd_launch_template.h:60-75).  Nothing for the host to manage: launches may   */
+/* overlap on different streams and may be captured in CUDA graphs (first call on a device       */
+/* outside the capture).                                                                         */
 /* ------------------------------------------------------------------------------------------- */
 typedef struct FaFwdParams {
   const void* q; /* dense (b, seqlen_q, h, d); varlen (total_q, h, d)                           */
@@ -279,6 +285,7 @@ int fa_combine(const FaCombineParams* p, fa_stream_t stream);
 /* lse_part[r] fp32 (b, h, seqlen_q) contiguous, -inf where rank r saw no key.  This call merges  */
 /* query rows [row_begin, row_begin + rows) of every sequence into o (b, rows, h, d) fp16 and     */
 /* lse (b, h, rows) fp32.  The caller orders the call after every rank has finished its partial.   */
+/* o and every o_part[r] must be 16-byte aligned.                                                   */
 /* ------------------------------------------------------------------------------------------- */
 #define FA_MAX_GATHER_PARTS 16
 typedef struct FaCombineGatherParams {
