@@ -201,7 +201,7 @@ NOISE_WMAX = 1e-2
 MEAN_FACTOR, MEAN_FACTOR_SMALL, SMALL_NUMEL = 1.25, 2.0, 32768
 MEAN_FACTOR_TINY, TINY_NUMEL = 3.0, 4096  # e.g. a single query row: a few rounding events decide the mean as well
 # Every comparison is recorded; with FA_PARITY_LOG=<file> the session writes the records there (conftest.py),
-# and with FA_PARITY_SOFT=1 the bounds are recorded without being asserted (to survey a new kernel in one run).
+# and with FA_PARITY_SOFT=1 the bounds are recorded without being asserted (to look over a new kernel in one run).
 PARITY_LOG: list = []
 _SOFT = os.environ.get("FA_PARITY_SOFT", "") == "1"
 
