@@ -617,3 +617,10 @@ def test_varlen_forward_many_ragged_sequences(ext, h, hk, d, causal):
         assert torch.equal(lse[i, :, :n], l1[0]), (i, n)
         assert lse[i, :, n:].abs().max().item() == 0 if n < max(lens) else True
     assert ext.device_status(True) == 0
+
+
+def test_package_reports_the_device_status_word(ext):
+    import flash_attention_turing_b200 as fa
+
+    assert fa.device_status() == 0
+    assert fa.device_status(reset=True) == 0
