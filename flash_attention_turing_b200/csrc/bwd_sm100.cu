@@ -120,7 +120,7 @@ bwd_dq_kernel(const __grid_constant__ BwdKernelParams p) {
   const int sk = varlen ? p.cu_seqlens_k[batch + 1] - k_off : p.seqlen_k;
   const int row0 = mblk * kBlock;
   if (row0 >= sq) return;
-  if (cta_should_stop(p.status)) return;
+  const int stop_probe = stop_probe_begin(p.status);  // consumed at the CTA-wide synchronisation below
   const int bq = varlen ? 0 : batch;
   const int head_k = head / (p.h / p.h_k);
   const int nkb = (sk + kBlock - 1) / kBlock;
@@ -177,13 +177,15 @@ bwd_dq_kernel(const __grid_constant__ BwdKernelParams p) {
     tmem_relinquish();
   }
   tc_fence_before_sync();
-  __syncthreads();
+  const bool stop = __syncthreads_or(stop_probe) != 0;  // sticky time-out bit set: the CTA does no work
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  if (stop && threadIdx.x == 0) bars->abort_flag = 1;  // the common exit then lets the loads issued above land
 
   // the last K block of a packed sequence holds rows of the next sequence (see zero_tile_rows_from)
   const bool fix_k_tail = varlen && (sk % kBlock) != 0 && nb == nkb && nb > 0;
-  if (warp == kProducerWarp) {
+  if (stop) {
+  } else if (warp == kProducerWarp) {
     if (lane == 0) {
       for (int j = n_early; j < nb; ++j)
         if (!load_kv(j)) break;
@@ -361,7 +363,7 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
   const int sk = varlen ? p.cu_seqlens_k[batch + 1] - k_off : p.seqlen_k;
   const int key0 = nblk * kBlock;
   if (key0 >= sk) return;
-  if (cta_should_stop(p.status)) return;
+  const int stop_probe = stop_probe_begin(p.status);
   const int bq = varlen ? 0 : batch;
   const int group = p.h / p.h_k;
   const int nq = (sq + kBlock - 1) / kBlock;
@@ -434,14 +436,16 @@ bwd_dkdv_kernel(const __grid_constant__ BwdKernelParams p) {
     tmem_relinquish();
   }
   tc_fence_before_sync();
-  __syncthreads();
+  const bool stop = __syncthreads_or(stop_probe) != 0;  // sticky time-out bit set: the CTA does no work
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  if (stop && threadIdx.x == 0) bars->abort_flag = 1;  // the common exit then lets the loads issued above land
 
   // the last Q / dO tile of a packed sequence holds rows of the next sequence (see zero_tile_rows_from)
   const bool fix_q_tail = kVarlen && (sq % kBlock) != 0 && n_it > 0;
   const int q_tail_rows = sq - (nq - 1) * kBlock;  // valid rows of the last Q tile
-  if (warp == kProducerWarp) {
+  if (stop) {
+  } else if (warp == kProducerWarp) {
     if (!fix_q_tail) {
       if (lane == 0) {
         for (int it = n_early; it < n_it; ++it)

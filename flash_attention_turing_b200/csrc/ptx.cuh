@@ -113,6 +113,13 @@ struct WaitCtx {
 // The wait-timeout bit of the status word is sticky (until the host clears it): a CTA that starts while it is
 // set does no work.  One thread reads the word and the answer is broadcast, so that the whole CTA takes the
 // same way out even if the bit is set while the CTA starts.
+// The same decision in two halves, for kernels that have a CTA-wide synchronisation early on anyway: thread 0
+// starts reading the word at the top of the kernel and the value is consumed by a __syncthreads_or at that
+// synchronisation, so the latency of the read overlaps the set-up instead of preceding it.
+__device__ __forceinline__ int stop_probe_begin(const int* status) {
+  return (threadIdx.x == 0 && status != nullptr) ? (*reinterpret_cast<const volatile int*>(status) & kStatusWaitTimeout) : 0;
+}
+
 __device__ __forceinline__ bool cta_should_stop(const int* status) {
   return __syncthreads_or(threadIdx.x == 0 && status != nullptr &&
                           (*reinterpret_cast<const volatile int*>(status) & kStatusWaitTimeout) != 0) != 0;

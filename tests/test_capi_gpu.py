@@ -222,6 +222,15 @@ def test_a_wait_that_runs_out_is_reported_and_the_context_stays_usable():
     capi.check(lib.fa_fwd(ctypes.byref(fp), _stream()))
     torch.cuda.synchronize()
     assert bool((o == 7.0).all())
+    # ... and so does a backward (its kernels take the decision at their first CTA-wide synchronisation)
+    dq, dk, dv = (torch.full_like(q, 7.0) for _ in range(3))
+    bp = capi.bwd_params(q, k, v, o, torch.ones_like(q), lse, dq, dk, dv, None, d ** -0.5, False)
+    need = lib.fa_bwd_workspace_bytes(ctypes.byref(bp))
+    ws = torch.empty(max(int(need), 1), dtype=torch.uint8, device=DEV)
+    bp.workspace, bp.workspace_bytes = ws.data_ptr(), need
+    capi.check(lib.fa_bwd(ctypes.byref(bp), _stream()))
+    torch.cuda.synchronize()
+    assert all(bool((x == 7.0).all()) for x in (dq, dk, dv))
     assert lib.fa_device_status(1) & 1  # read and clear
     assert lib.fa_device_status(0) == 0
     capi.check(lib.fa_fwd(ctypes.byref(fp), _stream()))
