@@ -222,3 +222,30 @@ def test_shard_chunks():
         sp.shard_chunks(0, 4, 36, "zigzag")
     with pytest.raises(ValueError):
         sp.shard_chunks(0, 4, 64, "striped")
+
+
+def test_owned_rows_balance_the_merge_under_a_causal_mask():
+    """Row ownership of the peer-read paths: one contiguous slice per rank, or the rows of the rank's two zig-zag
+    chunks.  The number of (row chunk, K/V chunk) pairs a rank has to fetch and merge under a causal mask -- a row
+    chunk sees the K/V chunks up to its own -- is the same on every rank only with the zig-zag rows."""
+    import torch
+
+    from flash_attention_turing_b200 import seq_parallel as sp
+
+    world, s = 8, 1024
+    assert sp.owned_rows(3, world, s) == [(384, 512)]
+    assert sp.owned_rows(3, world, s, "zigzag") == [(192, 256), (768, 832)]
+    c = s // (2 * world)
+
+    def pairs(rows):  # (row chunk, visible K/V chunk) pairs: row chunk i sees the K/V chunks 0 .. i
+        return sum(i + 1 for b, e in rows for i in range(b // c, e // c))
+
+    contiguous = [pairs(sp.owned_rows(r, world, s)) for r in range(world)]
+    zigzag = [pairs(sp.owned_rows(r, world, s, "zigzag")) for r in range(world)]
+    assert max(contiguous) == 31 and min(contiguous) == 3
+    assert set(zigzag) == {17}
+    x = torch.arange(s).view(1, s, 1, 1)
+    got = sp.gather_owned_rows(x, 3, world, "zigzag").flatten().tolist()
+    assert got == list(range(192, 256)) + list(range(768, 832))
+    every = sorted(v for r in range(world) for v in sp.gather_owned_rows(x, r, world, "zigzag").flatten().tolist())
+    assert every == list(range(s))
