@@ -35,6 +35,11 @@ struct BwdKernelParams {
   float* dq_acc;
   int64_t dq_acc_rows;  // rows per head
   int total_q;
+  // persistent dQ kernel: work counter pair (see next_sched_slot) and the extents of the index space
+  int* sched;
+  int items_x;      // dense: 128-row Q tiles per (sequence, head)
+  int total_items;  // dense: items_x * h * b; packed sequences: h * (total_q / 128 + b)
+  int b;
 };
 
 // Launchers of the single-kernel backward (bwd_fused_sm100.cu), called from fa_bwd_stages().
