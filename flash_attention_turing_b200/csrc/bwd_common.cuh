@@ -8,6 +8,7 @@
 // The backward kernels keep the wait loops inline: with 96 registers per thread a call inside their loops costs
 // spills around every wait (measured: dK/dV kernel 25 % slower at head size 128 with the out-of-line form).
 #define FA_WAIT_INLINE
+#define FA_WAIT_SLIM
 #include "ptx.cuh"
 
 namespace fa {

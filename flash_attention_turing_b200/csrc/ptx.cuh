@@ -136,6 +136,27 @@ __device__ __forceinline__ bool cta_should_stop(const int* status) {
 // the loops made up a sixth of the forward kernel's code, which runs close to the capacity of the instruction
 // cache (all warp roles execute different code at the same time; hit rate 82 % inline, 98 % out of line).
 #ifdef FA_WAIT_INLINE
+#ifdef FA_WAIT_SLIM
+// Smallest inline form (the backward kernels: thirty waits each, and their code size is throughput -- 6 KB less
+// code made them 2-6 % faster): the limit is a number of probes instead of wall time.  A probe of an incomplete
+// phase suspends the thread for 3.96 us (measured), so 2^20 probes are about 4 s; only the role of the waiting
+// warp is recorded with the time-out bit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
+  if (mbar_test(bar, parity)) return true;
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_test(bar, parity)) return true;
+    if (((++spins) & 0x3ff) == 0) {
+      if (*ctx.abort_flag) return false;
+      if (spins >= (1u << 20)) {
+        *ctx.abort_flag = 1;
+        if (ctx.status) atomicOr(ctx.status, kStatusWaitTimeout | ((ctx.tag & 0xff) << 8));
+        return false;
+      }
+    }
+  }
+}
+#else
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
   if (mbar_test(bar, parity)) return true;
   uint64_t t0 = 0;
@@ -161,6 +182,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   }
 }
 
+#endif
 __device__ __forceinline__ bool mbar_wait_hot(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
   return mbar_wait(bar, parity, ctx);
 }

@@ -63,7 +63,8 @@ int fa_abi_version(void);
  * host call reports FA_OK, until this function clears the word -- a host that wants to detect the condition
  * polls it.  When a wait gave up, bits 8-31 of the word identify the first one that did: bits 8-15 the warp
  * role that waited, bits 16-23 the index of the barrier in the kernel's barrier block, bit 24 the phase
- * parity, bits 25-30 the loop iteration.  No counterpart in the reference, whose launches are
+ * parity, bits 25-30 the loop iteration (the backward kernels record the role only).  No counterpart in the
+ * reference, whose launches are
  * not error-checked at all (src/flash_fwd_launch_template.h:73-89). */
 int fa_device_status(int reset);
 
