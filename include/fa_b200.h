@@ -87,7 +87,7 @@ int fa_selftest_wait_timeout(uint32_t limit_us, fa_stream_t stream);
 /* leaves it zero), where the reference launches one CTA per row block of a max_seqlen-sized     */
 /* grid (src/flash_fwd_launch_template.h:60-75).  Nothing for the host to manage: launches may   */
 /* overlap on different streams and may be captured in CUDA graphs (first call on a device       */
-/* outside the capture).                                                                         */
+/* outside the capture).  The dQ and dK/dV kernels of fa_bwd take their work the same way.       */
 /* ------------------------------------------------------------------------------------------- */
 typedef struct FaFwdParams {
   const void* q; /* dense (b, seqlen_q, h, d); varlen (total_q, h, d)                           */
